@@ -1,0 +1,63 @@
+"""ctypes view of libf2k_attn.so - exactly the entry points include/f2k_attn.h declares.
+
+Importing this module loads the in-tree library and raises if it is missing: the package
+has no other implementation to fall back on.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+from .build import LIB_PATH, build
+
+F2K_OK, F2K_ERR_INVALID, F2K_ERR_UNSUPPORTED, F2K_ERR_WORKSPACE, F2K_ERR_CUDA, F2K_ERR_DEVICE = range(6)
+
+
+class AttnConfig(C.Structure):
+    """struct f2k_attn_config"""
+    _fields_ = [("batch", C.c_int), ("seq_txt", C.c_int), ("seq_img", C.c_int),
+                ("n_heads", C.c_int), ("head_dim", C.c_int), ("scale", C.c_float)]
+
+
+def _declare(lib: C.CDLL) -> None:
+    vp, i, f, sz = C.c_void_p, C.c_int, C.c_float, C.c_size_t
+    lib.f2k_attn_create.restype = i
+    lib.f2k_attn_create.argtypes = [C.POINTER(AttnConfig), C.POINTER(vp)]
+    lib.f2k_attn_destroy.restype = None
+    lib.f2k_attn_destroy.argtypes = [vp]
+    lib.f2k_attn_last_error.restype = C.c_char_p
+    lib.f2k_attn_last_error.argtypes = [vp]
+    lib.f2k_attn_workspace_bytes.restype = sz
+    lib.f2k_attn_workspace_bytes.argtypes = [vp]
+    lib.f2k_attn_fused_workspace_bytes.restype = sz
+    lib.f2k_attn_fused_workspace_bytes.argtypes = [vp]
+    lib.f2k_attn_forward.restype = i
+    lib.f2k_attn_forward.argtypes = [vp] * 10 + [sz, vp]
+    lib.f2k_attn_forward_fused.restype = i
+    lib.f2k_attn_forward_fused.argtypes = [vp] * 15 + [f, vp, vp, vp, sz, vp]
+    lib.f2k_attn_forward_fused_host.restype = i
+    lib.f2k_attn_forward_fused_host.argtypes = [vp] * 15 + [f, vp, vp, vp]
+    lib.f2k_attn_device_status.restype = i
+    lib.f2k_attn_device_status.argtypes = [vp, C.POINTER(i)]
+    lib.f2k_rmsnorm_bf16.restype = i
+    lib.f2k_rmsnorm_bf16.argtypes = [vp, vp, vp, i, i, f, vp]
+    lib.f2k_rope_4axis_inplace_bf16.restype = i
+    lib.f2k_rope_4axis_inplace_bf16.argtypes = [vp, vp, vp, vp, i, i, i, vp]
+    lib.f2k_build_rope_4axis_tables.restype = i
+    lib.f2k_build_rope_4axis_tables.argtypes = [vp, i, vp, i, f, vp, vp]
+    lib.f2k_attn_version.restype = C.c_char_p
+    lib.f2k_attn_version.argtypes = []
+
+
+def load(path: Path | None = None) -> C.CDLL:
+    path = Path(path) if path else LIB_PATH
+    if not path.exists():
+        build()
+    if not path.exists():
+        raise ImportError(f"{path} is missing and could not be built; f2k_cuda_b200 has no fallback path")
+    lib = C.CDLL(str(path))
+    _declare(lib)
+    return lib
+
+
+lib = load()

@@ -1,0 +1,417 @@
+// Non-causal flash-attention forward for head_dim 128, bf16, written for sm_100a.
+//
+// One CTA owns a pair of 128-row query tiles of one (batch, head) and walks every
+// key/value tile of the attended sequence:
+//
+//   warp 8  (one lane)  TMA producer: Q tiles once, then K_j, V_j into a 4-slot
+//                       ring of 32 KiB shared-memory slots (mbarrier full/empty).
+//   warp 9  (one lane)  tcgen05.mma issuer:  S_t = Q_t K_j^T  (A, B from shared
+//                       memory, K-major, 128-byte swizzle) and O_t += P_t V_j
+//                       (A = P_t from tensor memory, B = V_j MN-major). S_0, S_1,
+//                       O_0, O_1 are 128-column fp32 accumulators in TMEM.
+//   warps 0-3 / 4-7     softmax group for tile 0 / tile 1: one thread per query
+//                       row (= TMEM lane). Reads S_t with tcgen05.ld, keeps the
+//                       row in registers, exponentiates in the log2 domain, writes
+//                       bf16 P_t over the first 64 columns of S_t, and accumulates
+//                       the row sum from the unrounded fp32 values.
+//
+// Issue order per key/value tile j:  S0_j, PV1_{j-1}, S1_j, PV0_j.  While one
+// softmax group works on its S, the tensor pipe runs the other tile's two MMAs.
+//
+// Online softmax with a lazy reference maximum: the exponent reference of a row
+// only moves when some row of the warp sees a tile maximum more than 2^8 above it;
+// then the group rescales its O rows in TMEM itself. That window is safe because
+// the commit that published S_t for tile j also covers PV_t of tile j-1, and
+// PV_t of tile j is not issued before the group hands over P_t.
+//
+// Arithmetic follows the reference flash kernel (F2K_CUDA
+// src/backend/cuda/attention.cu:601-757): scores scaled by `scale`, P rounded to
+// bf16 for the P.V product, the row sum taken from fp32 P, one bf16 rounding of O.
+//
+// Every wait is bounded; when one expires the CTA sets the status word, drains its
+// own copies and MMAs, frees its tensor memory and returns.
+
+#include "attn_launch.h"
+#include "ptx.cuh"
+
+#include <cuda_bf16.h>
+
+namespace f2k {
+
+using namespace f2k::ptx;
+
+namespace {
+
+constexpr int kThreads     = 384;
+constexpr int kLoaderWarp  = 8;
+constexpr int kMmaWarp     = 9;
+constexpr int kStages      = 4;
+constexpr uint32_t kTileBytes = kTileM * kHeadDim * 2;  // 32 KiB: one Q, K or V tile
+constexpr uint32_t kBoxBytes  = kTileBytes / 2;         // one 128 x 64 TMA box
+constexpr uint32_t kTmemCols  = 512;
+constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO0 = 256, kColO1 = 384;
+constexpr float kLazyThreshold = 8.0f;  // log2 units
+
+struct SmemCtl {
+    uint64_t q_full[2];
+    uint64_t kv_full[kStages];
+    uint64_t kv_empty[kStages];
+    uint64_t s_full[2];
+    uint64_t p_full[2];
+    uint64_t o_full[2];
+    uint64_t drain;
+    uint32_t tmem_base;
+    uint32_t abort;
+};
+
+constexpr uint32_t kSmemQ    = 0;
+constexpr uint32_t kSmemRing = 2 * kTileBytes;
+constexpr uint32_t kSmemCtl  = kSmemRing + kStages * kTileBytes;
+constexpr uint32_t kSmemUsed = kSmemCtl + sizeof(SmemCtl);
+
+template <int kMax>
+__device__ __forceinline__ void locate_tile(const int* tile_start, const int* len, int nseg,
+                                            int tile, int& seg, int& row0, int& valid) {
+    seg = 0;
+#pragma unroll
+    for (int i = 1; i < kMax; ++i)
+        if (i < nseg && tile >= tile_start[i]) seg = i;
+    row0  = (tile - tile_start[seg]) * kTileN;
+    valid = min(kTileN, len[seg] - row0);
+}
+
+// S_t = Q_t K^T: 8 k-steps of 16 over head_dim; both operands K-major, 128-byte
+// swizzle, stored as two 128 x 64 boxes (k-steps 0-3 in the first, 4-7 in the second).
+__device__ __forceinline__ void issue_qk(uint32_t d_tmem, uint32_t q_smem, uint32_t k_smem) {
+    constexpr uint32_t idesc = umma_idesc_bf16(kTileM, kTileN, /*b_mn_major=*/false);
+#pragma unroll
+    for (int kk = 0; kk < kHeadDim / 16; ++kk) {
+        const uint32_t off = (kk >> 2) * kBoxBytes + (kk & 3) * 32;
+        umma_ss(d_tmem, umma_smem_desc(q_smem + off, 16, 1024),
+                umma_smem_desc(k_smem + off, 16, 1024), idesc, kk > 0 ? 1u : 0u);
+    }
+}
+
+// O_t (+)= P_t V: 8 k-steps of 16 keys. A = P_t in TMEM (two bf16 per 32-bit column,
+// 8 columns per k-step); B = V tile, MN-major: head_dim contiguous in 64-element
+// (128-byte) swizzled rows, one row per key, the second 64 head-dim elements one box
+// (16 KiB) further on; 8-key groups are 1024 bytes apart.
+__device__ __forceinline__ void issue_pv(uint32_t d_tmem, uint32_t p_tmem, uint32_t v_smem,
+                                         bool accumulate) {
+    constexpr uint32_t idesc = umma_idesc_bf16(kTileM, kHeadDim, /*b_mn_major=*/true);
+#pragma unroll
+    for (int kk = 0; kk < kTileN / 16; ++kk) {
+        umma_ts(d_tmem, p_tmem + kk * 8, umma_smem_desc(v_smem + kk * 2048, kBoxBytes, 1024),
+                idesc, (accumulate || kk > 0) ? 1u : 0u);
+    }
+}
+
+}  // namespace
+
+__global__ void __launch_bounds__(kThreads, 1)
+attn_fwd_sm100_kernel(const __grid_constant__ AttnParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    const uint32_t smem     = (raw_addr + 1023u) & ~1023u;  // swizzle atoms need 1 KiB
+    SmemCtl* ctl = reinterpret_cast<SmemCtl*>(smem_raw + (smem - raw_addr) + kSmemCtl);
+    volatile uint32_t* abort_flag = &ctl->abort;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int pair = blockIdx.x;
+    const int head = blockIdx.y;
+    const int bidx = blockIdx.z;
+    const int n_kv = p.n_kv_tiles;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(smem_u32(&ctl->q_full[i]), 1);
+            mbar_init(smem_u32(&ctl->s_full[i]), 1);
+            mbar_init(smem_u32(&ctl->p_full[i]), 128);
+            mbar_init(smem_u32(&ctl->o_full[i]), 1);
+        }
+        for (int i = 0; i < kStages; ++i) {
+            mbar_init(smem_u32(&ctl->kv_full[i]), 1);
+            mbar_init(smem_u32(&ctl->kv_empty[i]), 1);
+        }
+        mbar_init(smem_u32(&ctl->drain), 1);
+        ctl->abort = 0;
+        fence_mbar_init();
+        fence_proxy_async_smem();
+    }
+    if (warp == kMmaWarp) {
+        tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(&ctl->tmem_base);
+
+    if (warp == kLoaderWarp) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            int issued = 0;
+            bool ok = true;
+            for (int t = 0; t < 2; ++t) {
+                const int qt = 2 * pair + t;
+                int seg, row0, valid;
+                if (qt < p.n_q_tiles) {
+                    locate_tile<kMaxQSeg>(p.q_tile_start, p.q_len, p.n_qseg, qt, seg, row0, valid);
+                } else {  // odd tile count: the spare tile reads zeros (out of bounds)
+                    seg = 0;
+                    row0 = ((p.q_len[0] + kTileM - 1) / kTileM) * kTileM;
+                }
+                const uint32_t bar = smem_u32(&ctl->q_full[t]);
+                const uint32_t dst = smem + kSmemQ + t * kTileBytes;
+                mbar_arrive_expect_tx(bar, kTileBytes);
+                tma_load_4d(dst, &p.tm_q[seg], bar, 0, head, row0, bidx);
+                tma_load_4d(dst + kBoxBytes, &p.tm_q[seg], bar, 64, head, row0, bidx);
+            }
+            for (int j = 0; j < n_kv && ok; ++j) {
+                int seg, row0, valid;
+                locate_tile<kMaxKvSeg>(p.kv_tile_start, p.kv_len, p.n_kvseg, j, seg, row0, valid);
+#pragma unroll
+                for (int kv = 0; kv < 2; ++kv) {
+                    const int slot = issued % kStages;
+                    const uint32_t par = (issued / kStages) & 1;
+                    ok = mbar_wait(smem_u32(&ctl->kv_empty[slot]), par ^ 1u, abort_flag);
+                    if (!ok) break;
+                    const uint32_t bar = smem_u32(&ctl->kv_full[slot]);
+                    const uint32_t dst = smem + kSmemRing + slot * kTileBytes;
+                    const CUtensorMap* tm = kv == 0 ? &p.tm_k[seg] : &p.tm_v[seg];
+                    mbar_arrive_expect_tx(bar, kTileBytes);
+                    tma_load_4d(dst, tm, bar, 0, head, row0, bidx);
+                    tma_load_4d(dst + kBoxBytes, tm, bar, 64, head, row0, bidx);
+                    ++issued;
+                }
+            }
+            if (!ok) {
+                // Leaving early: let the copies this thread started land first.
+                const uint64_t lim = 20000000ull;  // 20 ms each, still bounded
+                volatile uint32_t never = 0;
+                for (int t = 0; t < 2; ++t) mbar_wait(smem_u32(&ctl->q_full[t]), 0, &never, lim);
+                for (int i = max(0, issued - kStages); i < issued; ++i)
+                    mbar_wait(smem_u32(&ctl->kv_full[i % kStages]), (i / kStages) & 1, &never, lim);
+            }
+        }
+    } else if (warp == kMmaWarp) {
+        // ------------------------------ MMA issuer --------------------------------
+        if (lane == 0) {
+            const uint32_t q0 = smem + kSmemQ, q1 = q0 + kTileBytes;
+            bool ok = true;
+            // Ring slot of K_j is 2j, of V_j is 2j+1.
+            auto slot_addr = [&](int n) { return smem + kSmemRing + (n % kStages) * kTileBytes; };
+            auto wait_full = [&](int n) {
+                return mbar_wait(smem_u32(&ctl->kv_full[n % kStages]), (n / kStages) & 1, abort_flag);
+            };
+            auto release = [&](int n) { umma_commit(smem_u32(&ctl->kv_empty[n % kStages])); };
+
+            for (int j = 0; j < n_kv; ++j) {
+                // S0_j
+                if (!(ok = wait_full(2 * j))) break;
+                if (j == 0 && !(ok = mbar_wait(smem_u32(&ctl->q_full[0]), 0, abort_flag))) break;
+                tc_fence_after_sync();
+                issue_qk(tmem + kColS0, q0, slot_addr(2 * j));
+                umma_commit(smem_u32(&ctl->s_full[0]));
+                // PV1_{j-1}
+                if (j > 0) {
+                    if (!(ok = mbar_wait(smem_u32(&ctl->p_full[1]), (j - 1) & 1, abort_flag))) break;
+                    tc_fence_after_sync();
+                    issue_pv(tmem + kColO1, tmem + kColS1, slot_addr(2 * j - 1), j - 1 > 0);
+                    release(2 * j - 1);
+                }
+                // S1_j
+                if (j == 0 && !(ok = mbar_wait(smem_u32(&ctl->q_full[1]), 0, abort_flag))) break;
+                tc_fence_after_sync();
+                issue_qk(tmem + kColS1, q1, slot_addr(2 * j));
+                umma_commit(smem_u32(&ctl->s_full[1]));
+                release(2 * j);
+                // PV0_j
+                if (!(ok = wait_full(2 * j + 1))) break;
+                if (!(ok = mbar_wait(smem_u32(&ctl->p_full[0]), j & 1, abort_flag))) break;
+                tc_fence_after_sync();
+                issue_pv(tmem + kColO0, tmem + kColS0, slot_addr(2 * j + 1), j > 0);
+                if (j == n_kv - 1) umma_commit(smem_u32(&ctl->o_full[0]));
+            }
+            if (ok && n_kv > 0) {
+                // PV1 of the last tile
+                ok = mbar_wait(smem_u32(&ctl->p_full[1]), (n_kv - 1) & 1, abort_flag);
+                if (ok) {
+                    tc_fence_after_sync();
+                    issue_pv(tmem + kColO1, tmem + kColS1, slot_addr(2 * n_kv - 1), n_kv - 1 > 0);
+                    release(2 * n_kv - 1);
+                    umma_commit(smem_u32(&ctl->o_full[1]));
+                }
+            }
+            if (!ok) {
+                // Leaving early: wait (bounded) until the MMAs already issued retire, so
+                // tensor memory is idle when it is freed.
+                volatile uint32_t never = 0;
+                umma_commit(smem_u32(&ctl->drain));
+                mbar_wait(smem_u32(&ctl->drain), 0, &never, 20000000ull);
+            }
+        }
+    } else if (warp < 8) {
+        // ------------------------------ softmax groups -----------------------------
+        const int t = warp >> 2;                                   // which query tile
+        const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;  // this warp's TMEM lanes
+        const uint32_t tS = tmem + lane_base + (t == 0 ? kColS0 : kColS1);
+        const uint32_t tO = tmem + lane_base + (t == 0 ? kColO0 : kColO1);
+        const float c = p.scale_log2;
+
+        float m_ref = -INFINITY;  // exponent reference, in raw score units
+        float l_sum = 0.0f;
+        bool ok = true;
+
+        int kv_seg = 0, kv_row0 = 0;
+        for (int j = 0; j < n_kv; ++j) {
+            const int valid = min(kTileN, p.kv_len[kv_seg] - kv_row0);
+            kv_row0 += kTileN;
+            if (kv_row0 >= p.kv_len[kv_seg]) { kv_row0 = 0; ++kv_seg; }
+
+            ok = mbar_wait(smem_u32(&ctl->s_full[t]), j & 1, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after_sync();
+
+            uint32_t s[128];
+            {
+                uint32_t(&s0)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[0]);
+                uint32_t(&s1)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[32]);
+                uint32_t(&s2)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[64]);
+                uint32_t(&s3)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[96]);
+                tmem_ld_x32(tS + 0, s0);
+                tmem_ld_x32(tS + 32, s1);
+                tmem_ld_x32(tS + 64, s2);
+                tmem_ld_x32(tS + 96, s3);
+                tmem_wait_ld();
+            }
+            if (valid < kTileN) {  // last tile of a segment: keys past its end do not exist
+#pragma unroll
+                for (int i = 0; i < 128; ++i)
+                    if (i >= valid) s[i] = __float_as_uint(-INFINITY);
+            }
+
+            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < 128; i += 4) {
+                mx0 = fmaxf(mx0, __uint_as_float(s[i + 0]));
+                mx1 = fmaxf(mx1, __uint_as_float(s[i + 1]));
+                mx2 = fmaxf(mx2, __uint_as_float(s[i + 2]));
+                mx3 = fmaxf(mx3, __uint_as_float(s[i + 3]));
+            }
+            const float m_tile = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+
+            const bool need = (m_tile - m_ref) * c > kLazyThreshold;
+            if (__any_sync(0xffffffffu, need)) {
+                const float m_new = fmaxf(m_ref, m_tile);
+                const float f = ex2_approx((m_ref - m_new) * c);
+                l_sum *= f;
+                m_ref = m_new;
+                if (j > 0) {
+                    // Rescale this row of O in place (O_t is idle, see the file header).
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        uint32_t o[32];
+                        tmem_ld_x32(tO + q * 32, o);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
+                        tmem_st_x32(tO + q * 32, o);
+                    }
+                }
+            }
+
+            const float neg_mc = -m_ref * c;
+            float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                uint32_t pk[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 4) {
+                    const float p0 = ex2_approx(fmaf(__uint_as_float(s[q * 32 + i + 0]), c, neg_mc));
+                    const float p1 = ex2_approx(fmaf(__uint_as_float(s[q * 32 + i + 1]), c, neg_mc));
+                    const float p2 = ex2_approx(fmaf(__uint_as_float(s[q * 32 + i + 2]), c, neg_mc));
+                    const float p3 = ex2_approx(fmaf(__uint_as_float(s[q * 32 + i + 3]), c, neg_mc));
+                    sum0 += p0; sum1 += p1; sum2 += p2; sum3 += p3;
+                    pk[i / 2 + 0] = pack_bf16x2(p0, p1);
+                    pk[i / 2 + 1] = pack_bf16x2(p2, p3);
+                }
+                tmem_st_x16(tS + q * 16, pk);  // P_t aliases the first 64 columns of S_t
+            }
+            tmem_wait_st();
+            tc_fence_before_sync();
+            mbar_arrive(smem_u32(&ctl->p_full[t]));
+            l_sum += (sum0 + sum1) + (sum2 + sum3);
+        }
+
+        // ------------------------------ epilogue ------------------------------------
+        if (ok && n_kv > 0) {
+            ok = mbar_wait(smem_u32(&ctl->o_full[t]), 0, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+        }
+        if (ok && n_kv > 0) {
+            tc_fence_after_sync();
+            const int qt = 2 * pair + t;
+            int seg = 0, row0 = 0, valid = 0;
+            if (qt < p.n_q_tiles)
+                locate_tile<kMaxQSeg>(p.q_tile_start, p.q_len, p.n_qseg, qt, seg, row0, valid);
+            const int r = (warp & 3) * 32 + lane;  // row inside the tile
+            const float inv = 1.0f / (l_sum + 1e-30f);
+            __nv_bfloat16* orow = static_cast<__nv_bfloat16*>(p.o_ptr[seg]) +
+                                  (long long)bidx * p.o_batch_stride[seg] +
+                                  (long long)(row0 + r) * p.o_tok_stride[seg] +
+                                  (long long)head * kHeadDim;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                uint32_t o[32];
+                tmem_ld_x32(tO + q * 32, o);  // every lane takes part, valid row or not
+                tmem_wait_ld();
+                if (r < valid) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        uint4 v;
+                        v.x = pack_bf16x2(__uint_as_float(o[i + 0]) * inv, __uint_as_float(o[i + 1]) * inv);
+                        v.y = pack_bf16x2(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
+                        v.z = pack_bf16x2(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
+                        v.w = pack_bf16x2(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
+                        *reinterpret_cast<uint4*>(orow + q * 32 + i) = v;
+                    }
+                }
+            }
+        }
+    }
+
+    // ------------------------------ common exit ---------------------------------
+    __syncwarp();
+    tc_fence_before_sync();
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag != 0u && p.status != nullptr)
+        atomicOr(p.status, (int)kStatusWaitExpired);
+    if (warp == kMmaWarp) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem, kTmemCols);
+    }
+}
+
+size_t attn_fwd_smem_bytes() { return kSmemUsed + 1024; }
+
+cudaError_t attn_fwd_launch(const AttnParams& p, cudaStream_t stream) {
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    const size_t smem = attn_fwd_smem_bytes();
+    if (dev < 64 && !configured[dev]) {
+        e = cudaFuncSetAttribute(attn_fwd_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem);
+        if (e != cudaSuccess) return e;
+        configured[dev] = true;
+    }
+    dim3 grid((p.n_q_tiles + 1) / 2, p.n_heads, p.batch);
+    attn_fwd_sm100_kernel<<<grid, kThreads, smem, stream>>>(p);
+    return cudaPeekAtLastError();
+}
+
+}  // namespace f2k

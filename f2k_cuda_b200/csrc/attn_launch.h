@@ -1,0 +1,44 @@
+// Host-callable launchers of the CUDA kernels behind the C ABI (include/f2k_attn.h).
+#pragma once
+
+#include "attn_params.h"
+
+#include <cstddef>
+#include <cstdint>
+#include <cuda_runtime.h>
+
+namespace f2k {
+
+// tcgen05 flash-attention forward (attn_fwd_sm100.cu).
+size_t      attn_fwd_smem_bytes();
+cudaError_t attn_fwd_launch(const AttnParams& p, cudaStream_t stream);
+
+// Fused per-head RMSNorm + 4-axis RoPE for the Q and K of up to two streams in one
+// launch (qk_prologue.cu). One job per tensor; all jobs share head count and eps.
+struct QkPrologueJob {
+    const void*  x;        // [batch, seq, heads, 128] bf16, raw projection output
+    void*        y;        // same shape; may equal x
+    const void*  gamma;    // [128] bf16
+    const float* cos_tab;  // [seq, 64] fp32
+    const float* sin_tab;  // [seq, 64] fp32
+    int          seq;      // tokens per batch element
+    long long    rows;     // batch * seq * heads head-rows
+};
+constexpr int kMaxPrologueJobs = 4;
+struct QkPrologueParams {
+    QkPrologueJob job[kMaxPrologueJobs];
+    long long     row_start[kMaxPrologueJobs + 1];  // prefix sum of rows
+    int           n_jobs;
+    int           n_heads;
+    float         eps;
+};
+cudaError_t qk_prologue_launch(const QkPrologueParams& p, cudaStream_t stream);
+
+// Stand-alone kernels with the reference's call shapes (qk_prologue.cu).
+cudaError_t rmsnorm_rows_launch(const void* x, const void* gamma, void* y, int rows, int dim,
+                                float eps, cudaStream_t stream);
+cudaError_t rope4_rows_launch(void* x, const float* cos_tab, const float* sin_tab,
+                              const int32_t* pos_ids, int rows, int head_dim, int seq_max,
+                              cudaStream_t stream);
+
+}  // namespace f2k

@@ -1,0 +1,427 @@
+// Implementation of the C ABI declared in include/f2k_attn.h: argument checking,
+// TMA tensor-map construction, workspace carving and kernel launches. Everything that
+// touches the GPU lives in the kernels (attn_fwd_sm100.cu, qk_prologue.cu); there is
+// no CPU path here and none is reachable from these entry points.
+
+#include "f2k_attn.h"
+
+#include "attn_launch.h"
+
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <string>
+#include <vector>
+
+namespace {
+
+using namespace f2k;
+
+constexpr size_t kAlign = 256;
+inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver entry point is fetched through the runtime so that the library carries no
+// link-time dependency on libcuda.
+EncodeTiledFn encode_tiled_fn(std::string& err) {
+    static EncodeTiledFn fn = nullptr;
+    if (fn) return fn;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    const cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q);
+    if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || p == nullptr) {
+        err = std::string("cuTensorMapEncodeTiled unavailable: ") + cudaGetErrorString(e);
+        return nullptr;
+    }
+    fn = reinterpret_cast<EncodeTiledFn>(p);
+    return fn;
+}
+
+// One segment: bf16 [batch, len, heads, 128], token stride and batch stride in elements.
+bool encode_segment(CUtensorMap* map, const void* base, int len, int heads, int batch,
+                    long long tok_stride, long long batch_stride, std::string& err) {
+    EncodeTiledFn fn = encode_tiled_fn(err);
+    if (!fn) return false;
+    if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0) {
+        err = "tensor base pointer is not 16-byte aligned";
+        return false;
+    }
+    const cuuint64_t dims[4]    = {(cuuint64_t)kHeadDim, (cuuint64_t)heads, (cuuint64_t)len,
+                                   (cuuint64_t)batch};
+    const cuuint64_t strides[3] = {(cuuint64_t)kHeadDim * 2, (cuuint64_t)tok_stride * 2,
+                                   (cuuint64_t)batch_stride * 2};
+    const cuuint32_t box[4]     = {64, 1, (cuuint32_t)kTileM, 1};
+    const cuuint32_t estr[4]    = {1, 1, 1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims,
+                          strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        char buf[96];
+        std::snprintf(buf, sizeof buf, "cuTensorMapEncodeTiled failed (CUresult %d)", (int)r);
+        err = buf;
+        return false;
+    }
+    return true;
+}
+
+}  // namespace
+
+struct f2k_attn {
+    f2k_attn_config cfg{};
+    float           scale = 0.f;
+    bool            valid = false;
+    std::string     err;
+    int             device = -1;
+    int*            d_status = nullptr;
+
+    // Descriptors of the last forward call; rebuilt only when a pointer changes.
+    const void* last_in[6] = {};
+    void*       last_out[2] = {};
+    bool        have_params = false;
+    AttnParams  params;
+
+    // Device staging of the host-buffer entry point.
+    void*  stage = nullptr;
+    size_t stage_bytes = 0;
+
+    size_t bytes_txt() const {
+        return (size_t)cfg.batch * cfg.seq_txt * cfg.n_heads * cfg.head_dim * 2;
+    }
+    size_t bytes_img() const {
+        return (size_t)cfg.batch * cfg.seq_img * cfg.n_heads * cfg.head_dim * 2;
+    }
+    size_t fused_ws() const { return 2 * align_up(bytes_txt(), kAlign) + 2 * align_up(bytes_img(), kAlign); }
+};
+
+namespace {
+
+int fail(f2k_attn* h, int code, std::string msg) {
+    h->err = std::move(msg);
+    return code;
+}
+int fail_cuda(f2k_attn* h, const char* what, cudaError_t e) {
+    return fail(h, F2K_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
+}
+
+// Builds (or reuses) the launch parameters for attention over the text||image
+// segments held at the given pointers.
+int prepare_params(f2k_attn* h, const void* q_txt, const void* k_txt, const void* v_txt,
+                   const void* q_img, const void* k_img, const void* v_img, void* o_txt,
+                   void* o_img) {
+    const void* in[6] = {q_txt, k_txt, v_txt, q_img, k_img, v_img};
+    void* out[2]      = {o_txt, o_img};
+    if (h->have_params && std::memcmp(in, h->last_in, sizeof in) == 0 &&
+        std::memcmp(out, h->last_out, sizeof out) == 0)
+        return F2K_OK;
+    h->have_params = false;
+
+    const f2k_attn_config& c = h->cfg;
+    AttnParams& p = h->params;
+    std::memset(&p, 0, sizeof p);
+    const long long tok = (long long)c.n_heads * kHeadDim;
+
+    struct Seg { const void *q, *k, *v; void* o; int len; };
+    Seg segs[2];
+    int n = 0;
+    if (c.seq_txt > 0) segs[n++] = {q_txt, k_txt, v_txt, o_txt, c.seq_txt};
+    segs[n++] = {q_img, k_img, v_img, o_img, c.seq_img};
+
+    int tiles = 0;
+    for (int s = 0; s < n; ++s) {
+        const Seg& g = segs[s];
+        if (!g.q || !g.k || !g.v || !g.o) return fail(h, F2K_ERR_INVALID, "null tensor pointer");
+        if ((reinterpret_cast<uintptr_t>(g.o) & 15u) != 0)
+            return fail(h, F2K_ERR_INVALID, "output pointer is not 16-byte aligned");
+        const long long bstride = (long long)g.len * tok;
+        if (!encode_segment(&p.tm_q[s], g.q, g.len, c.n_heads, c.batch, tok, bstride, h->err) ||
+            !encode_segment(&p.tm_k[s], g.k, g.len, c.n_heads, c.batch, tok, bstride, h->err) ||
+            !encode_segment(&p.tm_v[s], g.v, g.len, c.n_heads, c.batch, tok, bstride, h->err))
+            return F2K_ERR_CUDA;
+        p.o_ptr[s]          = g.o;
+        p.o_tok_stride[s]   = tok;
+        p.o_batch_stride[s] = bstride;
+        p.q_len[s] = p.kv_len[s] = g.len;
+        p.q_tile_start[s] = p.kv_tile_start[s] = tiles;
+        tiles += (g.len + kTileM - 1) / kTileM;
+    }
+    p.q_tile_start[n] = p.kv_tile_start[n] = tiles;
+    p.n_qseg = p.n_kvseg = n;
+    p.n_q_tiles = p.n_kv_tiles = tiles;
+    p.n_heads    = c.n_heads;
+    p.batch      = c.batch;
+    p.scale_log2 = h->scale * 1.4426950408889634f;
+    p.status     = h->d_status;
+
+    std::memcpy(h->last_in, in, sizeof in);
+    std::memcpy(h->last_out, out, sizeof out);
+    h->have_params = true;
+    return F2K_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int f2k_attn_create(const f2k_attn_config* cfg, f2k_attn** out) {
+    if (!out) return F2K_ERR_INVALID;
+    *out = nullptr;
+    f2k_attn* h = new (std::nothrow) f2k_attn();
+    if (!h) return F2K_ERR_CUDA;
+    *out = h;
+    if (!cfg) return fail(h, F2K_ERR_INVALID, "null config");
+    h->cfg = *cfg;
+    // Same refusals, same wording, as the reference constructors.
+    if (cfg->batch <= 0 || cfg->seq_txt < 0 || cfg->seq_img <= 0 || cfg->n_heads <= 0 ||
+        cfg->head_dim <= 0)
+        return fail(h, F2K_ERR_INVALID,
+                    cfg->seq_txt != 0 ? "JointAttention: zero/negative dim" : "Attention: zero/negative dim");
+    if (cfg->head_dim != kHeadDim)
+        return fail(h, F2K_ERR_UNSUPPORTED,
+                    "head_dim must be 128: this engine implements only the MMDiT attention shape "
+                    "and has no fallback kernel for other head dims");
+    h->scale = cfg->scale > 0.f ? cfg->scale : 1.0f / std::sqrt((float)cfg->head_dim);
+
+    cudaError_t e = cudaGetDevice(&h->device);
+    if (e != cudaSuccess) return fail_cuda(h, "cudaGetDevice", e);
+    int major = 0;
+    e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, h->device);
+    if (e != cudaSuccess) return fail_cuda(h, "cudaDeviceGetAttribute", e);
+    if (major != 10)
+        return fail(h, F2K_ERR_UNSUPPORTED, "this library contains sm_100a code only (needs a B200-class GPU)");
+    e = cudaMalloc(reinterpret_cast<void**>(&h->d_status), sizeof(int));
+    if (e != cudaSuccess) return fail_cuda(h, "cudaMalloc(status)", e);
+    e = cudaMemset(h->d_status, 0, sizeof(int));
+    if (e != cudaSuccess) return fail_cuda(h, "cudaMemset(status)", e);
+    h->valid = true;
+    return F2K_OK;
+}
+
+void f2k_attn_destroy(f2k_attn* h) {
+    if (!h) return;
+    if (h->d_status) cudaFree(h->d_status);
+    if (h->stage) cudaFree(h->stage);
+    delete h;
+}
+
+const char* f2k_attn_last_error(const f2k_attn* h) { return h ? h->err.c_str() : "no handle"; }
+
+size_t f2k_attn_workspace_bytes(const f2k_attn* h) {
+    (void)h;
+    return 0;
+}
+
+size_t f2k_attn_fused_workspace_bytes(const f2k_attn* h) { return (h && h->valid) ? h->fused_ws() : 0; }
+
+int f2k_attn_forward(f2k_attn* h, const void* q_txt, const void* k_txt, const void* v_txt,
+                     const void* q_img, const void* k_img, const void* v_img, void* o_txt,
+                     void* o_img, void* workspace, size_t workspace_bytes, void* stream) {
+    (void)workspace;
+    (void)workspace_bytes;  // nothing to check: this path needs no workspace
+    if (!h) return F2K_ERR_INVALID;
+    if (!h->valid) return F2K_ERR_INVALID;  // keeps the creation error as last_error
+    const int rc = prepare_params(h, q_txt, k_txt, v_txt, q_img, k_img, v_img, o_txt, o_img);
+    if (rc != F2K_OK) return rc;
+    const cudaError_t e = attn_fwd_launch(h->params, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail_cuda(h, "attention launch", e);
+    return F2K_OK;
+}
+
+int f2k_attn_forward_fused(f2k_attn* h, const void* q_txt, const void* k_txt, const void* v_txt,
+                           const void* q_img, const void* k_img, const void* v_img,
+                           const void* gamma_q_txt, const void* gamma_k_txt,
+                           const void* gamma_q_img, const void* gamma_k_img, const float* cos_txt,
+                           const float* sin_txt, const float* cos_img, const float* sin_img,
+                           float eps, void* o_txt, void* o_img, void* workspace,
+                           size_t workspace_bytes, void* stream) {
+    if (!h) return F2K_ERR_INVALID;
+    if (!h->valid) return F2K_ERR_INVALID;
+    if (workspace_bytes < h->fused_ws() || !workspace)
+        return fail(h, F2K_ERR_WORKSPACE, "workspace too small");
+    const f2k_attn_config& c = h->cfg;
+    const bool has_txt = c.seq_txt > 0;
+    if (!q_img || !k_img || !gamma_q_img || !gamma_k_img || !cos_img || !sin_img ||
+        (has_txt && (!q_txt || !k_txt || !gamma_q_txt || !gamma_k_txt || !cos_txt || !sin_txt)))
+        return fail(h, F2K_ERR_INVALID, "null tensor pointer");
+
+    uint8_t* ws = static_cast<uint8_t*>(workspace);
+    void* qn_txt = ws;
+    void* kn_txt = ws + align_up(h->bytes_txt(), kAlign);
+    void* qn_img = ws + 2 * align_up(h->bytes_txt(), kAlign);
+    void* kn_img = static_cast<uint8_t*>(qn_img) + align_up(h->bytes_img(), kAlign);
+
+    QkPrologueParams pp;
+    std::memset(&pp, 0, sizeof pp);
+    int n = 0;
+    long long rows = 0;
+    auto add = [&](const void* x, void* y, const void* g, const float* ct, const float* st, int seq) {
+        QkPrologueJob& j = pp.job[n];
+        j.x = x; j.y = y; j.gamma = g; j.cos_tab = ct; j.sin_tab = st; j.seq = seq;
+        j.rows = (long long)c.batch * seq * c.n_heads;
+        pp.row_start[n] = rows;
+        rows += j.rows;
+        ++n;
+    };
+    if (has_txt) {
+        add(q_txt, qn_txt, gamma_q_txt, cos_txt, sin_txt, c.seq_txt);
+        add(k_txt, kn_txt, gamma_k_txt, cos_txt, sin_txt, c.seq_txt);
+    }
+    add(q_img, qn_img, gamma_q_img, cos_img, sin_img, c.seq_img);
+    add(k_img, kn_img, gamma_k_img, cos_img, sin_img, c.seq_img);
+    pp.row_start[n] = rows;
+    pp.n_jobs  = n;
+    pp.n_heads = c.n_heads;
+    pp.eps     = eps;
+
+    const int rc = prepare_params(h, has_txt ? qn_txt : nullptr, has_txt ? kn_txt : nullptr, v_txt,
+                                  qn_img, kn_img, v_img, o_txt, o_img);
+    if (rc != F2K_OK) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    cudaError_t e = qk_prologue_launch(pp, s);
+    if (e != cudaSuccess) return fail_cuda(h, "prologue launch", e);
+    e = attn_fwd_launch(h->params, s);
+    if (e != cudaSuccess) return fail_cuda(h, "attention launch", e);
+    return F2K_OK;
+}
+
+int f2k_attn_forward_fused_host(f2k_attn* h, const void* hq_txt, const void* hk_txt,
+                                const void* hv_txt, const void* hq_img, const void* hk_img,
+                                const void* hv_img, const void* gamma_q_txt,
+                                const void* gamma_k_txt, const void* gamma_q_img,
+                                const void* gamma_k_img, const float* cos_txt,
+                                const float* sin_txt, const float* cos_img, const float* sin_img,
+                                float eps, void* ho_txt, void* ho_img, void* stream) {
+    if (!h) return F2K_ERR_INVALID;
+    if (!h->valid) return F2K_ERR_INVALID;
+    const bool has_txt = h->cfg.seq_txt > 0;
+    if (!hq_img || !hk_img || !hv_img || !ho_img ||
+        (has_txt && (!hq_txt || !hk_txt || !hv_txt || !ho_txt)))
+        return fail(h, F2K_ERR_INVALID, "null host pointer");
+    const size_t bt = align_up(h->bytes_txt(), kAlign), bi = align_up(h->bytes_img(), kAlign);
+    const size_t need = 4 * bt + 4 * bi + h->fused_ws();
+    if (h->stage_bytes < need) {
+        if (h->stage) cudaFree(h->stage);
+        h->stage = nullptr;
+        h->stage_bytes = 0;
+        const cudaError_t e = cudaMalloc(&h->stage, need);
+        if (e != cudaSuccess) return fail_cuda(h, "cudaMalloc(staging)", e);
+        h->stage_bytes = need;
+    }
+    uint8_t* d = static_cast<uint8_t*>(h->stage);
+    void* dq_t = d;            void* dk_t = d + bt;       void* dv_t = d + 2 * bt;  void* do_t = d + 3 * bt;
+    uint8_t* di = d + 4 * bt;
+    void* dq_i = di;           void* dk_i = di + bi;      void* dv_i = di + 2 * bi; void* do_i = di + 3 * bi;
+    void* ws = di + 4 * bi;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    cudaError_t e = cudaSuccess;
+    auto h2d = [&](void* dst, const void* src, size_t n) {
+        if (e == cudaSuccess && n) e = cudaMemcpyAsync(dst, src, n, cudaMemcpyHostToDevice, s);
+    };
+    if (has_txt) {
+        h2d(dq_t, hq_txt, h->bytes_txt());
+        h2d(dk_t, hk_txt, h->bytes_txt());
+        h2d(dv_t, hv_txt, h->bytes_txt());
+    }
+    h2d(dq_i, hq_img, h->bytes_img());
+    h2d(dk_i, hk_img, h->bytes_img());
+    h2d(dv_i, hv_img, h->bytes_img());
+    if (e != cudaSuccess) return fail_cuda(h, "host-to-device copy", e);
+    const int rc = f2k_attn_forward_fused(h, has_txt ? dq_t : nullptr, has_txt ? dk_t : nullptr,
+                                          has_txt ? dv_t : nullptr, dq_i, dk_i, dv_i, gamma_q_txt,
+                                          gamma_k_txt, gamma_q_img, gamma_k_img, cos_txt, sin_txt,
+                                          cos_img, sin_img, eps, has_txt ? do_t : nullptr, do_i, ws,
+                                          h->fused_ws(), stream);
+    if (rc != F2K_OK) return rc;
+    if (has_txt) e = cudaMemcpyAsync(ho_txt, do_t, h->bytes_txt(), cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(ho_img, do_i, h->bytes_img(), cudaMemcpyDeviceToHost, s);
+    if (e != cudaSuccess) return fail_cuda(h, "device-to-host copy", e);
+    return F2K_OK;
+}
+
+int f2k_attn_device_status(f2k_attn* h, int* status_out) {
+    if (!h || !h->valid) return F2K_ERR_INVALID;
+    int st = 0;
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return fail_cuda(h, "cudaDeviceSynchronize", e);
+    e = cudaMemcpy(&st, h->d_status, sizeof st, cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return fail_cuda(h, "status read", e);
+    if (st != 0) {
+        e = cudaMemset(h->d_status, 0, sizeof st);
+        if (e != cudaSuccess) return fail_cuda(h, "status clear", e);
+    }
+    if (status_out) *status_out = st;
+    if (st != 0) return fail(h, F2K_ERR_DEVICE, "a bounded wait inside the attention kernel expired");
+    return F2K_OK;
+}
+
+int f2k_rmsnorm_bf16(const void* x, const void* gamma, void* y, int rows, int dim, float eps,
+                     void* stream) {
+    // Same refusals as the reference wrapper (kernels/rmsnorm.cu:76-77).
+    if (rows <= 0 || dim <= 0) return F2K_ERR_INVALID;
+    if (dim % 8 != 0) return F2K_ERR_INVALID;
+    if (!x || !gamma || !y) return F2K_ERR_INVALID;
+    return rmsnorm_rows_launch(x, gamma, y, rows, dim, eps, static_cast<cudaStream_t>(stream)) == cudaSuccess
+               ? F2K_OK : F2K_ERR_CUDA;
+}
+
+int f2k_rope_4axis_inplace_bf16(void* x, const float* cos_table, const float* sin_table,
+                                const int32_t* pos_ids, int rows, int head_dim, int seq_max,
+                                void* stream) {
+    // Same refusals as the reference wrapper (kernels/rope_4axis.cu:48-49).
+    if (rows <= 0 || head_dim <= 0 || (head_dim & 1)) return F2K_ERR_INVALID;
+    if (head_dim > 512) return F2K_ERR_INVALID;
+    if (!x || !cos_table || !sin_table || !pos_ids || seq_max <= 0) return F2K_ERR_INVALID;
+    return rope4_rows_launch(x, cos_table, sin_table, pos_ids, rows, head_dim, seq_max,
+                             static_cast<cudaStream_t>(stream)) == cudaSuccess
+               ? F2K_OK : F2K_ERR_CUDA;
+}
+
+int f2k_build_rope_4axis_tables(const int* axes_dim, int n_axes, const int* positions, int seq,
+                                float theta, float* cos_out, float* sin_out) {
+    if (!axes_dim || n_axes <= 0 || seq < 0 || (seq > 0 && (!positions || !cos_out || !sin_out)))
+        return F2K_ERR_INVALID;
+    int head_dim = 0;
+    for (int a = 0; a < n_axes; ++a) {
+        if (axes_dim[a] < 0) return F2K_ERR_INVALID;
+        head_dim += axes_dim[a];
+    }
+    const int half = head_dim / 2;
+    // Per axis a, pair k: frequency theta^(-2k/d_a) in double; angle = position * frequency;
+    // an axis fills d_a/2 consecutive pair slots of the token's row.
+    std::vector<double> freq((size_t)half > 0 ? half : 1);
+    std::vector<int> axis_of((size_t)half > 0 ? half : 1);
+    int off = 0;
+    for (int a = 0; a < n_axes; ++a) {
+        const int pairs = axes_dim[a] / 2;
+        for (int k = 0; k < pairs && off + k < half; ++k) {
+            freq[off + k]    = std::pow((double)theta, -2.0 * k / (double)axes_dim[a]);
+            axis_of[off + k] = a;
+        }
+        off += pairs;
+    }
+    const int filled = off < half ? off : half;
+    for (int s = 0; s < seq; ++s) {
+        float* cr = cos_out + (size_t)s * half;
+        float* sr = sin_out + (size_t)s * half;
+        for (int k = 0; k < half; ++k) {
+            if (k < filled) {
+                const double ang = (double)positions[(size_t)s * n_axes + axis_of[k]] * freq[k];
+                cr[k] = (float)std::cos(ang);
+                sr[k] = (float)std::sin(ang);
+            } else {  // odd axis widths leave trailing slots; the reference leaves them 0
+                cr[k] = 0.f;
+                sr[k] = 0.f;
+            }
+        }
+    }
+    return F2K_OK;
+}
+
+const char* f2k_attn_version(void) { return "f2k_attn sm_100a 0.1"; }
+
+}  // extern "C"

@@ -1,0 +1,154 @@
+/* f2k_attn.h - C ABI of the B200 (sm_100a) joint-attention engine.
+ *
+ * This library replaces ONE path of chrisjhebert1973/F2K_CUDA: the MMDiT joint
+ * attention of FLUX.2-klein (per-head QK-RMSNorm, 4-axis RoPE, non-causal attention
+ * over text||image tokens, 32 heads x head_dim 128, bf16). Each entry point below
+ * names the reference interface it stands in for (paths inside the reference tree).
+ *
+ * Conventions
+ *  - Every tensor pointer is a DEVICE pointer to contiguous bf16 laid out
+ *    [batch, seq, n_heads, head_dim] unless the function says "host".
+ *  - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream).
+ *  - Calls return 0 on success and a positive F2K_ERR_* code otherwise; nothing throws.
+ *    f2k_attn_last_error() gives a message that stays valid until the next call on
+ *    the same handle.
+ *  - forward calls are asynchronous on `stream`, never synchronise and never allocate
+ *    (the *_host variant allocates its staging buffers on its first call only).
+ *  - A handle holds mutable state (error text, cached TMA descriptors): use it from
+ *    one host thread at a time. Distinct handles on distinct streams are independent.
+ *  - There is no CPU fallback and no other GPU path: on a device that is not
+ *    compute capability 10.x, or for head_dim != 128, creation fails with a message.
+ */
+#ifndef F2K_ATTN_H
+#define F2K_ATTN_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct f2k_attn f2k_attn; /* opaque */
+
+enum {
+    F2K_OK              = 0,
+    F2K_ERR_INVALID     = 1, /* zero/negative dimension, null pointer */
+    F2K_ERR_UNSUPPORTED = 2, /* head_dim != 128, wrong GPU architecture */
+    F2K_ERR_WORKSPACE   = 3, /* workspace smaller than the *_workspace_bytes() value */
+    F2K_ERR_CUDA        = 4, /* a CUDA runtime/driver call failed; message has the detail */
+    F2K_ERR_DEVICE      = 5  /* a kernel reported a problem through the status word */
+};
+
+/* Shape of one attention module, fixed at creation like the reference's
+ * Attention::Config (src/backend/cuda/attention.h:31-37) and JointAttention::Config
+ * (src/backend/cuda/joint_attention.h:23-30).  seq_txt == 0 describes the plain
+ * self-attention module over seq_img tokens. */
+typedef struct f2k_attn_config {
+    int   batch;
+    int   seq_txt;
+    int   seq_img;
+    int   n_heads;
+    int   head_dim; /* 128 */
+    float scale;    /* <= 0 selects 1/sqrt(head_dim), as the reference does */
+} f2k_attn_config;
+
+/* Replaces Attention::Attention (src/backend/cuda/attention.cu:763-776) and
+ * JointAttention::JointAttention (src/backend/cuda/joint_attention.cu:78-112).
+ * *out is set to a handle whenever memory for it could be obtained, also on failure,
+ * so that the message can be read; a failed handle refuses every forward call. */
+int f2k_attn_create(const f2k_attn_config* cfg, f2k_attn** out);
+
+/* Replaces the destructors of both reference classes. NULL is allowed. */
+void f2k_attn_destroy(f2k_attn* h);
+
+/* Replaces Attention::last_error / JointAttention::last_error
+ * (src/backend/cuda/attention.cu:781, joint_attention.cu:117-119). */
+const char* f2k_attn_last_error(const f2k_attn* h);
+
+/* Replaces JointAttention::workspace_size_bytes (joint_attention.cu:120-122).
+ * The reference needs four concatenation buffers; this engine reads both streams in
+ * place, so the answer is 0 and f2k_attn_forward accepts workspace == NULL. */
+size_t f2k_attn_workspace_bytes(const f2k_attn* h);
+
+/* Workspace of f2k_attn_forward_fused: normalised+rotated copies of Q and K. */
+size_t f2k_attn_fused_workspace_bytes(const f2k_attn* h);
+
+/* Replaces JointAttention::forward (joint_attention.cu:124-167) and, with
+ * seq_txt == 0 and the *_txt pointers NULL, Attention::forward
+ * (attention.cu:887-927). Inputs are already normalised and rotated by the caller.
+ * O_txt/O_img receive softmax(scale * Q K^T) V over the text||image sequence. */
+int f2k_attn_forward(f2k_attn* h,
+                     const void* q_txt, const void* k_txt, const void* v_txt,
+                     const void* q_img, const void* k_img, const void* v_img,
+                     void* o_txt, void* o_img,
+                     void* workspace, size_t workspace_bytes, void* stream);
+
+/* The whole per-block sequence of the reference callers in one call
+ * (DoubleStreamBlock::forward, src/backend/cuda/double_stream_block.cu:290-379;
+ * SingleStreamBlock::forward, single_stream_block.cu:254-267): per-head RMSNorm of Q
+ * and K with the stream's gains, 4-axis RoPE with the stream's tables at position =
+ * token index, then joint attention. q and k are the raw projection outputs and are
+ * left untouched; V gets neither step. gamma_*: [128] bf16. cos/sin: fp32
+ * [seq, 64] as built by f2k_build_rope_4axis_tables. */
+int f2k_attn_forward_fused(f2k_attn* h,
+                           const void* q_txt, const void* k_txt, const void* v_txt,
+                           const void* q_img, const void* k_img, const void* v_img,
+                           const void* gamma_q_txt, const void* gamma_k_txt,
+                           const void* gamma_q_img, const void* gamma_k_img,
+                           const float* cos_txt, const float* sin_txt,
+                           const float* cos_img, const float* sin_img,
+                           float eps,
+                           void* o_txt, void* o_img,
+                           void* workspace, size_t workspace_bytes, void* stream);
+
+/* Same computation as f2k_attn_forward_fused with q, k, v, o in HOST memory (pinned
+ * memory makes the copies asynchronous); gains and tables stay device pointers, like
+ * the construction-time uploads of the reference. Copies in, computes and copies out
+ * on `stream` without synchronising. Device staging is allocated on the first call.
+ * No counterpart in the reference, whose callers always hold device buffers; it exists
+ * so that end-to-end time including host<->device traffic can be measured. */
+int f2k_attn_forward_fused_host(f2k_attn* h,
+                                const void* hq_txt, const void* hk_txt, const void* hv_txt,
+                                const void* hq_img, const void* hk_img, const void* hv_img,
+                                const void* gamma_q_txt, const void* gamma_k_txt,
+                                const void* gamma_q_img, const void* gamma_k_img,
+                                const float* cos_txt, const float* sin_txt,
+                                const float* cos_img, const float* sin_img,
+                                float eps,
+                                void* ho_txt, void* ho_img, void* stream);
+
+/* Reads and clears the device status word the kernels of this handle write
+ * (0 = clean). Synchronises the device. A non-zero word means a bounded wait inside
+ * a kernel expired and the last outputs must not be used; the call then returns
+ * F2K_ERR_DEVICE. No counterpart in the reference, which never checks for
+ * asynchronous kernel failure. */
+int f2k_attn_device_status(f2k_attn* h, int* status_out);
+
+/* Replaces rmsnorm_bf16 (src/backend/cuda/kernels/rmsnorm.cu:74-88):
+ * y = bf16(x * rsqrt(mean(x^2) + eps) * gamma) per row; y may alias x;
+ * dim must be a positive multiple of 8. */
+int f2k_rmsnorm_bf16(const void* x, const void* gamma, void* y,
+                     int rows, int dim, float eps, void* stream);
+
+/* Replaces rope_4axis_inplace_bf16 (src/backend/cuda/kernels/rope_4axis.cu:44-54):
+ * interleaved-pair rotation in place, position clamped to [0, seq_max-1];
+ * head_dim must be even and <= 512. */
+int f2k_rope_4axis_inplace_bf16(void* x, const float* cos_table, const float* sin_table,
+                                const int32_t* pos_ids, int rows, int head_dim, int seq_max,
+                                void* stream);
+
+/* Replaces build_rope_4axis_tables (src/backend/cuda/kernels/rope_4axis.cu:56-97).
+ * Host function. positions is [seq][n_axes] row-major; cos_out/sin_out receive
+ * [seq][sum(axes_dim)/2] fp32. */
+int f2k_build_rope_4axis_tables(const int* axes_dim, int n_axes,
+                                const int* positions, int seq, float theta,
+                                float* cos_out, float* sin_out);
+
+/* Library identification string (static storage). */
+const char* f2k_attn_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* F2K_ATTN_H */
