@@ -1,0 +1,422 @@
+#!/usr/bin/env python
+"""Benchmark of the joint-attention hot path (hd128, S = 4608: 512 text + 64x64 image tokens).
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One step = one pass of the hot path over one batch: fused QK-RMSNorm + 4-axis RoPE, then
+joint attention, through the C ABI. Work counted per step: 4 * B * H * S^2 * D flops (QK^T
+and PV only; norm, RoPE and softmax are not counted).
+
+N = 1: B = 1, 32 heads (the 1024px generation step). N > 1 (one process per GPU under
+torchrun): batch N with the 32 heads sharded 32/N per GPU, so every GPU still owns 32
+(batch, head) units - weak scaling, no collective on the data path.
+
+`value` is device-timed with inputs resident in HBM; `e2e` is the same step through the
+host-buffer entry point with pinned host tensors (H2D of Q, K, V and D2H of O inside the
+timed region). `roofline` times the attention kernel alone. `cpu_baseline` is the fp32 host
+restatement (oracle/) on a bounded head sample. `--impl reference` runs the reference's own
+CUDA kernels rebuilt for sm_100a (oracle/_ref) on the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+
+METRIC = "joint_attn_tflops"
+UNIT = "TFLOP/s"
+FALLBACK_PEAK_TFLOPS = 1590.0
+# DRAM bytes (read + write) of one attention-kernel launch at S=4608, B=1, H=32, from the ncu
+# capture summarised in profiles/ (None until captured).
+ATTN_DRAM_TRAFFIC_BYTES = None
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+def measured_peak():
+    f = ROOT / "MEASURED_PEAKS.json"
+    if f.exists():
+        try:
+            d = json.loads(f.read_text())
+            return float(d["bf16_tflops"]), "measured bf16_tflops (cuBLAS burst, MEASURED_PEAKS.json)"
+        except Exception:
+            pass
+    return FALLBACK_PEAK_TFLOPS, "fallback 1590 TFLOP/s (MEASURED_PEAKS.json absent)"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled while the timed regions run."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device: int):
+        self.proc = None
+        try:
+            uuid = str(torch.cuda.get_device_properties(device).uuid)
+            if not uuid.startswith("GPU-"):
+                uuid = "GPU-" + uuid
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", uuid, f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except Exception:
+            self.proc.kill()
+            out = ""
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0])); mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        top = max(sm)
+        load = [x for x in sm if x >= 0.6 * top]       # samples taken while kernels ran
+        return {"sm_mhz": statistics.median(load), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def dev_bf16(bits):
+    return torch.from_numpy(np.ascontiguousarray(bits).view(np.int16)).view(torch.bfloat16).cuda()
+
+
+def pinned(bits):
+    return torch.from_numpy(np.ascontiguousarray(bits).view(np.int16)).view(torch.bfloat16).pin_memory()
+
+
+def time_region(fn, steps, stream):
+    """Milliseconds per step of `fn` called `steps` times, CUDA events on the launching stream."""
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record(stream)
+    for _ in range(steps):
+        fn()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def make_rank_problem(n_gpus: int, rank: int):
+    """Host tensors of this rank: batch n_gpus, heads [rank*32/n, (rank+1)*32/n)."""
+    from f2k_cuda_b200.inputs import SEED_BASE, Workload, make_problem
+    heads = 32 // n_gpus
+    w = Workload("s4608", n_gpus, 512, ((64, 64),), seed=SEED_BASE + 1)
+    # every rank draws its own heads: same distribution, rank-dependent seed keeps it cheap
+    wl = Workload("s4608", n_gpus, 512, ((64, 64),), n_heads=heads, seed=SEED_BASE + 1 + 1000 * rank)
+    return w, make_problem(wl)
+
+
+def cpu_baseline(problem, tabs, flops_per_head):
+    """fp32 host restatement (oracle/, OpenMP) on a bounded sample of heads of the same workload."""
+    import oracle
+    orc = oracle.load_oracle()
+    p = problem
+    D = p.w.head_dim
+    H = p.q_img.shape[2]
+
+    def run(h0, h1):
+        t0 = time.perf_counter()
+        prep = {}
+        for name, x, g, (cos, sin), seq in (("q_txt", p.q_txt, p.gammas[0], tabs[0:2], p.w.seq_txt),
+                                            ("k_txt", p.k_txt, p.gammas[1], tabs[0:2], p.w.seq_txt),
+                                            ("q_img", p.q_img, p.gammas[2], tabs[2:4], p.w.seq_img),
+                                            ("k_img", p.k_img, p.gammas[3], tabs[2:4], p.w.seq_img)):
+            xs = np.ascontiguousarray(x[:1, :, h0:h1])
+            n = xs.shape[2]
+            y = orc.rmsnorm_bf16(xs.reshape(-1, D), g, 1e-6)
+            pos = ((np.arange(seq * n) // n) % seq).astype(np.int32)
+            prep[name] = orc.rope_bf16(y, cos, sin, pos, seq).reshape(1, seq, n, D)
+        q = np.concatenate([prep["q_txt"], prep["q_img"]], 1)
+        k = np.concatenate([prep["k_txt"], prep["k_img"]], 1)
+        v = np.concatenate([p.v_txt[:1, :, h0:h1], p.v_img[:1, :, h0:h1]], 1)
+        orc.attention_f32(q, k, v)
+        return time.perf_counter() - t0
+
+    t1 = run(0, 1)                                   # calibration: one head
+    n = int(max(1, min(H, 15.0 / max(t1, 1e-3))))   # about 15 s of CPU work
+    t = run(0, n)
+    return {"value": n * flops_per_head / t / 1e12, "unit": UNIT, "cores": orc.threads, "kind": "port",
+            "sample": f"batch element 0, heads 0..{n - 1} of {H} (S=4608): QK-norm + RoPE + fp32 attention, {t:.1f} s"}
+
+
+def run_ours(args, rank, world):
+    import f2k_cuda_b200 as f2k
+    dev = torch.cuda.current_device()
+    stream = torch.cuda.current_stream()
+    w, p = make_rank_problem(world, rank)
+    H = p.q_img.shape[2]
+    B, St, Si, D = w.batch, w.seq_txt, w.seq_img, w.head_dim
+    flops = 4.0 * B * H * (St + Si) ** 2 * D        # per GPU per step
+    tabs = (*f2k.build_rope_4axis_tables((32,) * 4, p.pos_txt, 2000.0),
+            *f2k.build_rope_4axis_tables((32,) * 4, p.pos_img, 2000.0))
+    ja = f2k.JointAttention(f2k.JointAttention.Config(B, St, Si, H, D))
+    if not ja.ok():
+        raise RuntimeError(ja.last_error())
+    host = [p.q_txt, p.k_txt, p.v_txt, p.q_img, p.k_img, p.v_img]
+    d = [dev_bf16(x) for x in host]
+    dg = [dev_bf16(g) for g in p.gammas]
+    dtab = [torch.from_numpy(t).cuda() for t in tabs]
+    o_t, o_i = torch.empty_like(d[0]), torch.empty_like(d[3])
+    ws = torch.empty(ja.fused_workspace_size_bytes(), dtype=torch.uint8, device="cuda")
+
+    def step():
+        if not ja.forward_fused(*d, dg, dtab, 1e-6, o_t, o_i, ws):
+            raise RuntimeError(ja.last_error())
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    if ja.device_status() != 0:
+        raise RuntimeError("attention kernel reported a device-side error during warm-up")
+
+    sampler = ClockSampler(dev) if rank == 0 else None
+    if world > 1:
+        torch.distributed.barrier()
+    ms = time_region(step, args.steps, stream)
+    if world > 1:
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        ms = float(t.item())
+
+    # ---- the attention kernel alone (roofline), on the normalised Q/K the prologue left in ws
+    bt = (d[0].numel() * 2 + 255) // 256 * 256
+    bi = (d[3].numel() * 2 + 255) // 256 * 256
+    qn_t = ws[0:bt].view(torch.bfloat16)[: d[0].numel()].view_as(d[0])
+    kn_t = ws[bt:2 * bt].view(torch.bfloat16)[: d[0].numel()].view_as(d[0])
+    qn_i = ws[2 * bt:2 * bt + bi].view(torch.bfloat16)[: d[3].numel()].view_as(d[3])
+    kn_i = ws[2 * bt + bi:2 * bt + 2 * bi].view(torch.bfloat16)[: d[3].numel()].view_as(d[3])
+
+    def attn_only():
+        if not ja.forward(qn_t, kn_t, d[2], qn_i, kn_i, d[5], o_t, o_i, None, 0):
+            raise RuntimeError(ja.last_error())
+
+    for _ in range(3):
+        attn_only()
+    ms_attn = time_region(attn_only, args.steps, stream)
+
+    # ---- end to end through host buffers
+    hin = [pinned(x) for x in host]
+    ho_t, ho_i = torch.empty_like(hin[0]).pin_memory(), torch.empty_like(hin[3]).pin_memory()
+
+    def step_host():
+        if not ja.forward_fused_host(*hin, dg, dtab, 1e-6, ho_t, ho_i):
+            raise RuntimeError(ja.last_error())
+
+    for _ in range(3):
+        step_host()
+    torch.cuda.synchronize()
+    if world > 1:
+        torch.distributed.barrier()
+    e2e_steps = max(3, min(args.steps, 20))
+    ms_e2e = time_region(step_host, e2e_steps, stream)
+    if world > 1:
+        t = torch.tensor([ms_e2e], device="cuda", dtype=torch.float64)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        ms_e2e = float(t.item())
+    clocks = sampler.stop() if sampler else None
+    status = ja.device_status()
+    if status != 0:
+        raise RuntimeError("attention kernel reported a device-side error")
+    if rank != 0:
+        return None
+
+    peak, peak_src = measured_peak()
+    achieved = flops / (ms_attn * 1e-3) / 1e12
+    in_bytes = sum(x.numel() * 2 for x in hin)
+    out_bytes = ho_t.numel() * 2 + ho_i.numel() * 2
+    line = {
+        "metric": METRIC, "value": world * flops / (ms * 1e-3) / 1e12, "unit": UNIT,
+        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": "s4608 joint attention (512 text + 64x64 image tokens, hd128), "
+                               f"batch {B}, {H} heads per GPU" + (" (heads sharded)" if world > 1 else ""),
+                   "step": "fused QK-RMSNorm + 4-axis RoPE + non-causal attention, one call",
+                   "flops_per_step_per_gpu": flops, "seq": St + Si, "head_dim": D,
+                   "l2": "inputs + outputs + workspace of a step exceed the 126 MB L2 (226 MB)",
+                   "parallelism": f"heads{world}" if world > 1 else "single"},
+        "per_gpu_tflops": flops / (ms * 1e-3) / 1e12,
+        "pct_of_peak": 100.0 * flops / (ms * 1e-3) / 1e12 / peak,
+        "roofline": {"bound": "tensor", "kernel": "attn_fwd_sm100_kernel", "achieved": achieved, "peak": peak,
+                     "unit": UNIT, "frac": achieved / peak, "traffic": ATTN_DRAM_TRAFFIC_BYTES,
+                     "ms_per_launch": ms_attn, "peak_source": peak_src},
+        "e2e": {"value": world * flops / (ms_e2e * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms_e2e,
+                "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": out_bytes, "steps": e2e_steps},
+        "gpu_launches": 2 * args.steps,
+        "clocks": clocks,
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline(p, tabs, flops / H)
+    return line
+
+
+def run_reference(args, rank, world):
+    """The reference's own implementation of the path: its CUDA kernels (rmsnorm_bf16 x4,
+    rope_4axis_inplace_bf16 x4, JointAttention::forward with its concat/split copies), rebuilt
+    unmodified for sm_100a. It has no CPU implementation and no multi-GPU code: rank 0 runs the
+    one-GPU workload, other ranks leave."""
+    if rank != 0:
+        return None
+    import oracle
+    ref = oracle.load_ref()
+    if ref is None:
+        return {"impl": "reference", "unavailable": "oracle/_ref/libf2k_ref.so not built (no reference checkout at build time)"}
+    L = ref.lib
+    dev = torch.cuda.current_device()
+    stream = torch.cuda.current_stream()
+    w, p = make_rank_problem(1, 0)
+    B, St, Si, H, D = w.batch, w.seq_txt, w.seq_img, w.n_heads, w.head_dim
+    flops = 4.0 * B * H * (St + Si) ** 2 * D
+    (ct, st) = ref.build_rope_tables((32,) * 4, p.pos_txt, 2000.0)
+    (ci, si) = ref.build_rope_tables((32,) * 4, p.pos_img, 2000.0)
+    host = [p.q_txt, p.k_txt, p.v_txt, p.q_img, p.k_img, p.v_img]
+    src = [dev_bf16(x) for x in host]
+    d = [torch.empty_like(x) for x in src]
+    dg = [dev_bf16(g) for g in p.gammas]
+    dtab = [torch.from_numpy(t).cuda() for t in (ct, st, ci, si)]
+    pos_t = ((torch.arange(B * St * H, device="cuda") // H) % St).to(torch.int32)
+    pos_i = ((torch.arange(B * Si * H, device="cuda") // H) % Si).to(torch.int32)
+    o_t, o_i = torch.empty_like(d[0]), torch.empty_like(d[3])
+    h = L.f2k_ref_joint_create(B, St, Si, H, D, 0.0)
+    if not L.f2k_ref_joint_ok(h):
+        return {"impl": "reference", "unavailable": "reference JointAttention refused the shape"}
+    ws_bytes = L.f2k_ref_joint_workspace_bytes(h)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device="cuda")
+    P = lambda t: C.c_void_p(t.data_ptr())  # noqa: E731
+    s_ptr = C.c_void_p(stream.cuda_stream)
+    launches = [0]
+
+    def compute():
+        ok = 1
+        for x, g, (c_, s_), pos, seq in ((d[0], dg[0], dtab[0:2], pos_t, St), (d[1], dg[1], dtab[0:2], pos_t, St),
+                                         (d[3], dg[2], dtab[2:4], pos_i, Si), (d[4], dg[3], dtab[2:4], pos_i, Si)):
+            rows = B * seq * H
+            ok &= L.f2k_ref_rmsnorm_bf16(P(x), P(g), P(x), rows, D, 1e-6, s_ptr)
+            ok &= L.f2k_ref_rope_4axis_inplace_bf16(P(x), P(c_), P(s_), P(pos), rows, D, seq, s_ptr)
+        ok &= L.f2k_ref_joint_forward(h, P(d[0]), P(d[1]), P(d[2]), P(d[3]), P(d[4]), P(d[5]), P(o_t), P(o_i),
+                                      P(ws), ws_bytes, s_ptr)
+        launches[0] += 13
+        if not ok:
+            raise RuntimeError("reference launch failed")
+
+    def step():
+        # the reference normalises in place, so each step starts from a fresh copy of the raw q, k
+        for dst, s_ in zip(d, src):
+            dst.copy_(s_, non_blocking=True)
+        compute()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    sampler = ClockSampler(dev)
+    launches[0] = 0
+    ms = time_region(step, args.steps, stream)
+    n_launch = launches[0]
+    # the device-to-device refresh copies are not part of the reference's path: time them alone and take them out
+    ms_copy = time_region(lambda: [dst.copy_(s_, non_blocking=True) for dst, s_ in zip(d, src)], args.steps, stream)
+    ms_path = max(ms - ms_copy, 1e-6)
+
+    hin = [pinned(x) for x in host]
+    ho_t, ho_i = torch.empty_like(hin[0]).pin_memory(), torch.empty_like(hin[3]).pin_memory()
+
+    def step_host():
+        for dst, s_ in zip(d, hin):
+            dst.copy_(s_, non_blocking=True)
+        compute()
+        ho_t.copy_(o_t, non_blocking=True)
+        ho_i.copy_(o_i, non_blocking=True)
+
+    for _ in range(2):
+        step_host()
+    e2e_steps = max(3, min(args.steps, 20))
+    ms_e2e = time_region(step_host, e2e_steps, stream)
+    clocks = sampler.stop()
+    L.f2k_ref_joint_destroy(h)
+    peak, peak_src = measured_peak()
+    val = flops / (ms_path * 1e-3) / 1e12
+    return {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_path, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "s4608 joint attention (512 text + 64x64 image tokens, hd128), batch 1, 32 heads",
+                   "step": "reference kernels rebuilt for sm_100a: rmsnorm_bf16 x4, rope_4axis_inplace_bf16 x4, "
+                           "JointAttention::forward (3 concat + flash_mma_kernel<128> + split)",
+                   "flops_per_step_per_gpu": flops, "ranks_used": 1,
+                   "note": "the reference's implementation of this path is CUDA only (no CPU code, no multi-GPU code)"},
+        "pct_of_peak": 100.0 * val / peak, "peak_source": peak_src,
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": 0, "kind": "reference",
+                         "sample": "not a CPU run: the reference has no CPU implementation of this path; its own CUDA "
+                                   "kernels, rebuilt for sm_100a, on one GPU, full workload"},
+        "e2e": {"value": flops / (ms_e2e * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms_e2e,
+                "h2d_bytes_per_step": sum(x.numel() * 2 for x in hin),
+                "d2h_bytes_per_step": ho_t.numel() * 2 + ho_i.numel() * 2, "steps": e2e_steps},
+        "gpu_launches": n_launch, "clocks": clocks,
+    }
+
+
+def main():
+    args = parse_args()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    if args.gpus > 1 and world == 1:
+        raise SystemExit("for --gpus N > 1 launch with: python -m torch.distributed.run --nnodes=1 "
+                         "--nproc-per-node N --master-addr 127.0.0.1 --master-port P bench.py --gpus N ...")
+    if 32 % world != 0:
+        raise SystemExit("the 32 heads shard over 1, 2, 4, 8, 16 or 32 GPUs")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a GPU: the library has no CPU path")
+    torch.cuda.set_device(local)
+    if args.impl == "reference" and rank != 0:
+        return
+    if world > 1 and args.impl == "ours":
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local))
+    try:
+        line = run_ours(args, rank, world) if args.impl == "ours" else run_reference(args, rank, world)
+        if line is not None:
+            print(json.dumps(line), flush=True)
+    finally:
+        if world > 1 and args.impl == "ours" and torch.distributed.is_initialized():
+            torch.distributed.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
