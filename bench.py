@@ -50,7 +50,9 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the timed CPU leg")
+    ap.add_argument("--skip-e2e", action="store_true",
+                    help="skip the host-buffer leg (for short profiler captures; the line then has e2e null)")
     return ap.parse_args()
 
 
@@ -231,24 +233,26 @@ def run_ours(args, rank, world):
     ms_attn = time_region(attn_only, args.steps, stream)
 
     # ---- end to end through host buffers
-    hin = [pinned(x) for x in host]
-    ho_t, ho_i = torch.empty_like(hin[0]).pin_memory(), torch.empty_like(hin[3]).pin_memory()
+    ms_e2e, e2e_steps = None, 0
+    hin = [pinned(x) for x in host] if not args.skip_e2e else []
+    if not args.skip_e2e:
+        ho_t, ho_i = torch.empty_like(hin[0]).pin_memory(), torch.empty_like(hin[3]).pin_memory()
 
-    def step_host():
-        if not ja.forward_fused_host(*hin, dg, dtab, 1e-6, ho_t, ho_i):
-            raise RuntimeError(ja.last_error())
+        def step_host():
+            if not ja.forward_fused_host(*hin, dg, dtab, 1e-6, ho_t, ho_i):
+                raise RuntimeError(ja.last_error())
 
-    for _ in range(3):
-        step_host()
-    torch.cuda.synchronize()
-    if world > 1:
-        torch.distributed.barrier()
-    e2e_steps = max(3, min(args.steps, 20))
-    ms_e2e = time_region(step_host, e2e_steps, stream)
-    if world > 1:
-        t = torch.tensor([ms_e2e], device="cuda", dtype=torch.float64)
-        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
-        ms_e2e = float(t.item())
+        for _ in range(3):
+            step_host()
+        torch.cuda.synchronize()
+        if world > 1:
+            torch.distributed.barrier()
+        e2e_steps = max(3, min(args.steps, 20))
+        ms_e2e = time_region(step_host, e2e_steps, stream)
+        if world > 1:
+            t = torch.tensor([ms_e2e], device="cuda", dtype=torch.float64)
+            torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+            ms_e2e = float(t.item())
     clocks = sampler.stop() if sampler else None
     status = ja.device_status()
     if status != 0:
@@ -258,8 +262,8 @@ def run_ours(args, rank, world):
 
     peak, peak_src = measured_peak()
     achieved = flops / (ms_attn * 1e-3) / 1e12
-    in_bytes = sum(x.numel() * 2 for x in hin)
-    out_bytes = ho_t.numel() * 2 + ho_i.numel() * 2
+    in_bytes = sum(x.numel() * 2 for x in d)
+    out_bytes = o_t.numel() * 2 + o_i.numel() * 2
     line = {
         "metric": METRIC, "value": world * flops / (ms * 1e-3) / 1e12, "unit": UNIT,
         "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
@@ -276,7 +280,8 @@ def run_ours(args, rank, world):
         "roofline": {"bound": "tensor", "kernel": "attn_fwd_sm100_kernel", "achieved": achieved, "peak": peak,
                      "unit": UNIT, "frac": achieved / peak, "traffic": ATTN_DRAM_TRAFFIC_BYTES,
                      "ms_per_launch": ms_attn, "peak_source": peak_src},
-        "e2e": {"value": world * flops / (ms_e2e * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms_e2e,
+        "e2e": None if ms_e2e is None else
+               {"value": world * flops / (ms_e2e * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": out_bytes, "steps": e2e_steps},
         "gpu_launches": 2 * args.steps,
         "clocks": clocks,

@@ -52,12 +52,24 @@ constexpr uint32_t kTmemCols  = 512;
 constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO0 = 256, kColO1 = 384;
 constexpr float kLazyThreshold = 8.0f;  // log2 units
 
+// Tuning switches (compile-time; the defaults are what ships).
+#ifndef F2K_OPT_SETMAXNREG
+#define F2K_OPT_SETMAXNREG 1   // softmax warpgroups take registers from the load/MMA warpgroup
+#endif
+#ifndef F2K_OPT_PACKED
+#define F2K_OPT_PACKED 1       // f32x2 FMA/ADD and 3-input max in the softmax
+#endif
+#ifndef F2K_OPT_SPLIT_P
+#define F2K_OPT_SPLIT_P 1      // hand P to the MMA warp in two 64-key halves
+#endif
+constexpr int kRegsSoftmax = 208, kRegsOther = 88;   // 2*128*208 + 128*88 = 64512 <= 384*168
+
 struct SmemCtl {
     uint64_t q_full[2];
     uint64_t kv_full[kStages];
     uint64_t kv_empty[kStages];
     uint64_t s_full[2];
-    uint64_t p_full[2];
+    uint64_t p_full[2][2];   // [tile][key half]
     uint64_t o_full[2];
     uint64_t drain;
     uint32_t tmem_base;
@@ -96,11 +108,13 @@ __device__ __forceinline__ void issue_qk(uint32_t d_tmem, uint32_t q_smem, uint3
 // 8 columns per k-step); B = V tile, MN-major: head_dim contiguous in 64-element
 // (128-byte) swizzled rows, one row per key, the second 64 head-dim elements one box
 // (16 KiB) further on; 8-key groups are 1024 bytes apart.
-__device__ __forceinline__ void issue_pv(uint32_t d_tmem, uint32_t p_tmem, uint32_t v_smem,
-                                         bool accumulate) {
+// `half` selects k-steps 0-3 (keys 0-63) or 4-7 (keys 64-127).
+__device__ __forceinline__ void issue_pv_half(uint32_t d_tmem, uint32_t p_tmem, uint32_t v_smem,
+                                              int half, bool accumulate) {
     constexpr uint32_t idesc = umma_idesc_bf16(kTileM, kHeadDim, /*b_mn_major=*/true);
 #pragma unroll
-    for (int kk = 0; kk < kTileN / 16; ++kk) {
+    for (int k4 = 0; k4 < 4; ++k4) {
+        const int kk = half * 4 + k4;
         umma_ts(d_tmem, p_tmem + kk * 8, umma_smem_desc(v_smem + kk * 2048, kBoxBytes, 1024),
                 idesc, (accumulate || kk > 0) ? 1u : 0u);
     }
@@ -127,7 +141,8 @@ attn_fwd_sm100_kernel(const __grid_constant__ AttnParams p) {
         for (int i = 0; i < 2; ++i) {
             mbar_init(smem_u32(&ctl->q_full[i]), 1);
             mbar_init(smem_u32(&ctl->s_full[i]), 1);
-            mbar_init(smem_u32(&ctl->p_full[i]), 128);
+            mbar_init(smem_u32(&ctl->p_full[i][0]), 128);
+            mbar_init(smem_u32(&ctl->p_full[i][1]), 128);
             mbar_init(smem_u32(&ctl->o_full[i]), 1);
         }
         for (int i = 0; i < kStages; ++i) {
@@ -148,113 +163,128 @@ attn_fwd_sm100_kernel(const __grid_constant__ AttnParams p) {
     tc_fence_after_sync();
     const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(&ctl->tmem_base);
 
-    if (warp == kLoaderWarp) {
-        // ------------------------------ TMA producer ------------------------------
-        if (lane == 0) {
-            int issued = 0;
-            bool ok = true;
-            for (int t = 0; t < 2; ++t) {
-                const int qt = 2 * pair + t;
-                int seg, row0, valid;
-                if (qt < p.n_q_tiles) {
-                    locate_tile<kMaxQSeg>(p.q_tile_start, p.q_len, p.n_qseg, qt, seg, row0, valid);
-                } else {  // odd tile count: the spare tile reads zeros (out of bounds)
-                    seg = 0;
-                    row0 = ((p.q_len[0] + kTileM - 1) / kTileM) * kTileM;
-                }
-                const uint32_t bar = smem_u32(&ctl->q_full[t]);
-                const uint32_t dst = smem + kSmemQ + t * kTileBytes;
-                mbar_arrive_expect_tx(bar, kTileBytes);
-                tma_load_4d(dst, &p.tm_q[seg], bar, 0, head, row0, bidx);
-                tma_load_4d(dst + kBoxBytes, &p.tm_q[seg], bar, 64, head, row0, bidx);
-            }
-            for (int j = 0; j < n_kv && ok; ++j) {
-                int seg, row0, valid;
-                locate_tile<kMaxKvSeg>(p.kv_tile_start, p.kv_len, p.n_kvseg, j, seg, row0, valid);
-#pragma unroll
-                for (int kv = 0; kv < 2; ++kv) {
-                    const int slot = issued % kStages;
-                    const uint32_t par = (issued / kStages) & 1;
-                    ok = mbar_wait(smem_u32(&ctl->kv_empty[slot]), par ^ 1u, abort_flag);
-                    if (!ok) break;
-                    const uint32_t bar = smem_u32(&ctl->kv_full[slot]);
-                    const uint32_t dst = smem + kSmemRing + slot * kTileBytes;
-                    const CUtensorMap* tm = kv == 0 ? &p.tm_k[seg] : &p.tm_v[seg];
+    if (warp >= 8) {
+        // ===================== warpgroup 2: TMA producer, MMA issuer, two idle warps =====================
+#if F2K_OPT_SETMAXNREG
+        setmaxnreg_dec<kRegsOther>();
+#endif
+        if (warp == kLoaderWarp) {
+            // ------------------------------ TMA producer ------------------------------
+            if (lane == 0) {
+                int issued = 0;
+                bool ok = true;
+                for (int t = 0; t < 2; ++t) {
+                    const int qt = 2 * pair + t;
+                    int seg, row0, valid;
+                    if (qt < p.n_q_tiles) {
+                        locate_tile<kMaxQSeg>(p.q_tile_start, p.q_len, p.n_qseg, qt, seg, row0, valid);
+                    } else {  // odd tile count: the spare tile reads zeros (out of bounds)
+                        seg = 0;
+                        row0 = ((p.q_len[0] + kTileM - 1) / kTileM) * kTileM;
+                    }
+                    const uint32_t bar = smem_u32(&ctl->q_full[t]);
+                    const uint32_t dst = smem + kSmemQ + t * kTileBytes;
                     mbar_arrive_expect_tx(bar, kTileBytes);
-                    tma_load_4d(dst, tm, bar, 0, head, row0, bidx);
-                    tma_load_4d(dst + kBoxBytes, tm, bar, 64, head, row0, bidx);
-                    ++issued;
+                    tma_load_4d(dst, &p.tm_q[seg], bar, 0, head, row0, bidx);
+                    tma_load_4d(dst + kBoxBytes, &p.tm_q[seg], bar, 64, head, row0, bidx);
+                }
+                for (int j = 0; j < n_kv && ok; ++j) {
+                    int seg, row0, valid;
+                    locate_tile<kMaxKvSeg>(p.kv_tile_start, p.kv_len, p.n_kvseg, j, seg, row0, valid);
+    #pragma unroll
+                    for (int kv = 0; kv < 2; ++kv) {
+                        const int slot = issued % kStages;
+                        const uint32_t par = (issued / kStages) & 1;
+                        ok = mbar_wait(smem_u32(&ctl->kv_empty[slot]), par ^ 1u, abort_flag);
+                        if (!ok) break;
+                        const uint32_t bar = smem_u32(&ctl->kv_full[slot]);
+                        const uint32_t dst = smem + kSmemRing + slot * kTileBytes;
+                        const CUtensorMap* tm = kv == 0 ? &p.tm_k[seg] : &p.tm_v[seg];
+                        mbar_arrive_expect_tx(bar, kTileBytes);
+                        tma_load_4d(dst, tm, bar, 0, head, row0, bidx);
+                        tma_load_4d(dst + kBoxBytes, tm, bar, 64, head, row0, bidx);
+                        ++issued;
+                    }
+                }
+                if (!ok) {
+                    // Leaving early: let the copies this thread started land first.
+                    const uint64_t lim = 20000000ull;  // 20 ms each, still bounded
+                    volatile uint32_t never = 0;
+                    for (int t = 0; t < 2; ++t) mbar_wait(smem_u32(&ctl->q_full[t]), 0, &never, lim);
+                    for (int i = max(0, issued - kStages); i < issued; ++i)
+                        mbar_wait(smem_u32(&ctl->kv_full[i % kStages]), (i / kStages) & 1, &never, lim);
                 }
             }
-            if (!ok) {
-                // Leaving early: let the copies this thread started land first.
-                const uint64_t lim = 20000000ull;  // 20 ms each, still bounded
-                volatile uint32_t never = 0;
-                for (int t = 0; t < 2; ++t) mbar_wait(smem_u32(&ctl->q_full[t]), 0, &never, lim);
-                for (int i = max(0, issued - kStages); i < issued; ++i)
-                    mbar_wait(smem_u32(&ctl->kv_full[i % kStages]), (i / kStages) & 1, &never, lim);
-            }
-        }
-    } else if (warp == kMmaWarp) {
-        // ------------------------------ MMA issuer --------------------------------
-        if (lane == 0) {
-            const uint32_t q0 = smem + kSmemQ, q1 = q0 + kTileBytes;
-            bool ok = true;
-            // Ring slot of K_j is 2j, of V_j is 2j+1.
-            auto slot_addr = [&](int n) { return smem + kSmemRing + (n % kStages) * kTileBytes; };
-            auto wait_full = [&](int n) {
-                return mbar_wait(smem_u32(&ctl->kv_full[n % kStages]), (n / kStages) & 1, abort_flag);
-            };
-            auto release = [&](int n) { umma_commit(smem_u32(&ctl->kv_empty[n % kStages])); };
+        } else if (warp == kMmaWarp) {
+            // ------------------------------ MMA issuer --------------------------------
+            if (lane == 0) {
+                const uint32_t q0 = smem + kSmemQ, q1 = q0 + kTileBytes;
+                bool ok = true;
+                // Ring slot of K_j is 2j, of V_j is 2j+1.
+                auto slot_addr = [&](int n) { return smem + kSmemRing + (n % kStages) * kTileBytes; };
+                auto wait_full = [&](int n) {
+                    return mbar_wait(smem_u32(&ctl->kv_full[n % kStages]), (n / kStages) & 1, abort_flag);
+                };
+                auto release = [&](int n) { umma_commit(smem_u32(&ctl->kv_empty[n % kStages])); };
+                // O_t (+)= P_t V_n, issued half by half as the softmax group hands P over.
+                auto issue_pv = [&](int t, int jj) -> bool {
+                    const uint32_t d = tmem + (t == 0 ? kColO0 : kColO1);
+                    const uint32_t a = tmem + (t == 0 ? kColS0 : kColS1);
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        if (!mbar_wait(smem_u32(&ctl->p_full[t][half]), jj & 1, abort_flag)) return false;
+                        tc_fence_after_sync();
+                        issue_pv_half(d, a, slot_addr(2 * jj + 1), half, jj > 0);
+                    }
+                    return true;
+                };
 
-            for (int j = 0; j < n_kv; ++j) {
-                // S0_j
-                if (!(ok = wait_full(2 * j))) break;
-                if (j == 0 && !(ok = mbar_wait(smem_u32(&ctl->q_full[0]), 0, abort_flag))) break;
-                tc_fence_after_sync();
-                issue_qk(tmem + kColS0, q0, slot_addr(2 * j));
-                umma_commit(smem_u32(&ctl->s_full[0]));
-                // PV1_{j-1}
-                if (j > 0) {
-                    if (!(ok = mbar_wait(smem_u32(&ctl->p_full[1]), (j - 1) & 1, abort_flag))) break;
+                for (int j = 0; j < n_kv; ++j) {
+                    // S0_j
+                    if (!(ok = wait_full(2 * j))) break;
+                    if (j == 0 && !(ok = mbar_wait(smem_u32(&ctl->q_full[0]), 0, abort_flag))) break;
                     tc_fence_after_sync();
-                    issue_pv(tmem + kColO1, tmem + kColS1, slot_addr(2 * j - 1), j - 1 > 0);
-                    release(2 * j - 1);
-                }
-                // S1_j
-                if (j == 0 && !(ok = mbar_wait(smem_u32(&ctl->q_full[1]), 0, abort_flag))) break;
-                tc_fence_after_sync();
-                issue_qk(tmem + kColS1, q1, slot_addr(2 * j));
-                umma_commit(smem_u32(&ctl->s_full[1]));
-                release(2 * j);
-                // PV0_j
-                if (!(ok = wait_full(2 * j + 1))) break;
-                if (!(ok = mbar_wait(smem_u32(&ctl->p_full[0]), j & 1, abort_flag))) break;
-                tc_fence_after_sync();
-                issue_pv(tmem + kColO0, tmem + kColS0, slot_addr(2 * j + 1), j > 0);
-                if (j == n_kv - 1) umma_commit(smem_u32(&ctl->o_full[0]));
-            }
-            if (ok && n_kv > 0) {
-                // PV1 of the last tile
-                ok = mbar_wait(smem_u32(&ctl->p_full[1]), (n_kv - 1) & 1, abort_flag);
-                if (ok) {
+                    issue_qk(tmem + kColS0, q0, slot_addr(2 * j));
+                    umma_commit(smem_u32(&ctl->s_full[0]));
+                    // PV1_{j-1}
+                    if (j > 0) {
+                        if (!(ok = issue_pv(1, j - 1))) break;
+                        release(2 * j - 1);
+                    }
+                    // S1_j
+                    if (j == 0 && !(ok = mbar_wait(smem_u32(&ctl->q_full[1]), 0, abort_flag))) break;
                     tc_fence_after_sync();
-                    issue_pv(tmem + kColO1, tmem + kColS1, slot_addr(2 * n_kv - 1), n_kv - 1 > 0);
-                    release(2 * n_kv - 1);
-                    umma_commit(smem_u32(&ctl->o_full[1]));
+                    issue_qk(tmem + kColS1, q1, slot_addr(2 * j));
+                    umma_commit(smem_u32(&ctl->s_full[1]));
+                    release(2 * j);
+                    // PV0_j
+                    if (!(ok = wait_full(2 * j + 1))) break;
+                    if (!(ok = issue_pv(0, j))) break;
+                    if (j == n_kv - 1) umma_commit(smem_u32(&ctl->o_full[0]));
                 }
-            }
-            if (!ok) {
-                // Leaving early: wait (bounded) until the MMAs already issued retire, so
-                // tensor memory is idle when it is freed.
-                volatile uint32_t never = 0;
-                umma_commit(smem_u32(&ctl->drain));
-                mbar_wait(smem_u32(&ctl->drain), 0, &never, 20000000ull);
+                if (ok && n_kv > 0) {
+                    // PV1 of the last tile
+                    ok = issue_pv(1, n_kv - 1);
+                    if (ok) {
+                        release(2 * n_kv - 1);
+                        umma_commit(smem_u32(&ctl->o_full[1]));
+                    }
+                }
+                if (!ok) {
+                    // Leaving early: wait (bounded) until the MMAs already issued retire, so
+                    // tensor memory is idle when it is freed.
+                    volatile uint32_t never = 0;
+                    umma_commit(smem_u32(&ctl->drain));
+                    mbar_wait(smem_u32(&ctl->drain), 0, &never, 20000000ull);
+                }
             }
         }
-    } else if (warp < 8) {
-        // ------------------------------ softmax groups -----------------------------
-        const int t = warp >> 2;                                   // which query tile
+    } else {
+        // ===================== warpgroups 0 and 1: softmax for query tile 0 / 1 =====================
+#if F2K_OPT_SETMAXNREG
+        setmaxnreg_inc<kRegsSoftmax>();
+#endif
+        const int t = warp >> 2;                                       // which query tile
         const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;  // this warp's TMEM lanes
         const uint32_t tS = tmem + lane_base + (t == 0 ? kColS0 : kColS1);
         const uint32_t tO = tmem + lane_base + (t == 0 ? kColO0 : kColO1);
@@ -294,6 +324,15 @@ attn_fwd_sm100_kernel(const __grid_constant__ AttnParams p) {
             }
 
             float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#if F2K_OPT_PACKED
+#pragma unroll
+            for (int i = 0; i < 128; i += 8) {
+                mx0 = fmax3(mx0, __uint_as_float(s[i + 0]), __uint_as_float(s[i + 1]));
+                mx1 = fmax3(mx1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
+                mx2 = fmax3(mx2, __uint_as_float(s[i + 4]), __uint_as_float(s[i + 5]));
+                mx3 = fmax3(mx3, __uint_as_float(s[i + 6]), __uint_as_float(s[i + 7]));
+            }
+#else
 #pragma unroll
             for (int i = 0; i < 128; i += 4) {
                 mx0 = fmaxf(mx0, __uint_as_float(s[i + 0]));
@@ -301,6 +340,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ AttnParams p) {
                 mx2 = fmaxf(mx2, __uint_as_float(s[i + 2]));
                 mx3 = fmaxf(mx3, __uint_as_float(s[i + 3]));
             }
+#endif
             const float m_tile = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
 
             const bool need = (m_tile - m_ref) * c > kLazyThreshold;
@@ -323,6 +363,8 @@ attn_fwd_sm100_kernel(const __grid_constant__ AttnParams p) {
                 }
             }
 
+            // P = 2^(c s - c m_ref), rounded to bf16 into the first 64 columns of S_t (two keys
+            // per column); the row sum keeps the unrounded values.
             const float neg_mc = -m_ref * c;
             float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
 #pragma unroll
@@ -330,19 +372,44 @@ attn_fwd_sm100_kernel(const __grid_constant__ AttnParams p) {
                 uint32_t pk[16];
 #pragma unroll
                 for (int i = 0; i < 32; i += 4) {
-                    const float p0 = ex2_approx(fmaf(__uint_as_float(s[q * 32 + i + 0]), c, neg_mc));
-                    const float p1 = ex2_approx(fmaf(__uint_as_float(s[q * 32 + i + 1]), c, neg_mc));
-                    const float p2 = ex2_approx(fmaf(__uint_as_float(s[q * 32 + i + 2]), c, neg_mc));
-                    const float p3 = ex2_approx(fmaf(__uint_as_float(s[q * 32 + i + 3]), c, neg_mc));
+                    float x0, x1, x2, x3;
+#if F2K_OPT_PACKED
+                    fma2(x0, x1, __uint_as_float(s[q * 32 + i + 0]), __uint_as_float(s[q * 32 + i + 1]),
+                         c, c, neg_mc, neg_mc);
+                    fma2(x2, x3, __uint_as_float(s[q * 32 + i + 2]), __uint_as_float(s[q * 32 + i + 3]),
+                         c, c, neg_mc, neg_mc);
+#else
+                    x0 = fmaf(__uint_as_float(s[q * 32 + i + 0]), c, neg_mc);
+                    x1 = fmaf(__uint_as_float(s[q * 32 + i + 1]), c, neg_mc);
+                    x2 = fmaf(__uint_as_float(s[q * 32 + i + 2]), c, neg_mc);
+                    x3 = fmaf(__uint_as_float(s[q * 32 + i + 3]), c, neg_mc);
+#endif
+                    const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
+                    const float p2 = ex2_approx(x2), p3 = ex2_approx(x3);
+#if F2K_OPT_PACKED
+                    add2(sum0, sum1, sum0, sum1, p0, p1);
+                    add2(sum2, sum3, sum2, sum3, p2, p3);
+#else
                     sum0 += p0; sum1 += p1; sum2 += p2; sum3 += p3;
+#endif
                     pk[i / 2 + 0] = pack_bf16x2(p0, p1);
                     pk[i / 2 + 1] = pack_bf16x2(p2, p3);
                 }
-                tmem_st_x16(tS + q * 16, pk);  // P_t aliases the first 64 columns of S_t
+                tmem_st_x16(tS + q * 16, pk);
+#if F2K_OPT_SPLIT_P
+                if (q == 1 || q == 3) {   // keys 0-63, then keys 64-127, are ready for the MMA warp
+                    tmem_wait_st();
+                    tc_fence_before_sync();
+                    mbar_arrive(smem_u32(&ctl->p_full[t][q >> 1]));
+                }
+#endif
             }
+#if !F2K_OPT_SPLIT_P
             tmem_wait_st();
             tc_fence_before_sync();
-            mbar_arrive(smem_u32(&ctl->p_full[t]));
+            mbar_arrive(smem_u32(&ctl->p_full[t][0]));
+            mbar_arrive(smem_u32(&ctl->p_full[t][1]));
+#endif
             l_sum += (sum0 + sum1) + (sum2 + sum3);
         }
 

@@ -195,6 +195,7 @@ def test_golden_reference_kernel_outputs(orc):
     in its reference-rounding mode."""
     from tests.golden.make_golden import gpu_cases, regenerate_inputs
     g = _golden_cases()
+    report = {}
     for case in gpu_cases():
         inp = regenerate_inputs(case)
         tag = case["tag"]
@@ -204,12 +205,18 @@ def test_golden_reference_kernel_outputs(orc):
             assert np.max(np.abs(got - ref)) <= 0.0625 * np.max(np.abs(ref)) * 2 ** -6, tag  # <= 1 bf16 ulp
             assert np.mean(got != ref) < 0.01, tag
         elif case["kind"] == "rope":
-            got = orc.rope_bf16(inp["x"], inp["cos"], inp["sin"], inp["pos_ids"], case["seq"])
+            cos, sin = orc.build_rope_tables((32,) * 4, inp["pos"], 2000.0)
+            got = orc.rope_bf16(inp["x"], cos, sin, inp["pos_ids"], case["seq"])
             assert np.mean(got != g[f"{tag}_y"]) < 0.01, tag
+            assert np.max(np.abs(from_bf16_bits(got) - from_bf16_bits(g[f"{tag}_y"]))) < 0.04, tag
         else:
             kw = dict(q_img=inp["q_img"], k_img=inp["k_img"], v_img=inp["v_img"])
             if case["seq_txt"]:
                 kw.update(q_txt=inp["q_txt"], k_txt=inp["k_txt"], v_txt=inp["v_txt"])
+            if case["prologue"]:
+                from tests.golden.make_golden import path_tables
+                tab_t, tab_i = path_tables(case, orc.build_rope_tables)
+                kw.update(gammas=inp["gammas"], tables=(*tab_t, *tab_i), eps=1e-6)
             for mode, tol in ((oracle.IDEAL, 2e-2), (oracle.REF_ROUND, 8e-3)):
                 o_t, o_i = orc.joint_path(mode=mode, **kw)
                 max_abs, cos, rel = metrics(o_i, from_bf16_bits(g[f"{tag}_o_img"]))
