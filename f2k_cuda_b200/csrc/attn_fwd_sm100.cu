@@ -1,19 +1,22 @@
 // Non-causal flash-attention forward for head_dim 128, bf16, written for sm_100a.
 //
 // One CTA owns a pair of 128-row query tiles of one (batch, head) and walks every
-// key/value tile of the attended sequence:
+// key/value tile of the attended sequence. Three warpgroups:
 //
-//   warp 8  (one lane)  TMA producer: Q tiles once, then K_j, V_j into a 4-slot
-//                       ring of 32 KiB shared-memory slots (mbarrier full/empty).
-//   warp 9  (one lane)  tcgen05.mma issuer:  S_t = Q_t K_j^T  (A, B from shared
-//                       memory, K-major, 128-byte swizzle) and O_t += P_t V_j
-//                       (A = P_t from tensor memory, B = V_j MN-major). S_0, S_1,
-//                       O_0, O_1 are 128-column fp32 accumulators in TMEM.
 //   warps 0-3 / 4-7     softmax group for tile 0 / tile 1: one thread per query
 //                       row (= TMEM lane). Reads S_t with tcgen05.ld, keeps the
 //                       row in registers, exponentiates in the log2 domain, writes
-//                       bf16 P_t over the first 64 columns of S_t, and accumulates
-//                       the row sum from the unrounded fp32 values.
+//                       bf16 P_t over the first 64 columns of S_t (handed to the MMA
+//                       warp in parts, so P_t V_j starts before the row is finished)
+//                       and accumulates the row sum from the unrounded fp32 values.
+//   warp 8  (one lane)  TMA producer: Q tiles once, then K_j, V_j into a 4-slot
+//                       ring of 32 KiB shared-memory slots (mbarrier full/empty).
+//   warp 9  (converged) tcgen05.mma issuer:  S_t = Q_t K_j^T  (A, B from shared
+//                       memory, K-major, 128-byte swizzle) and O_t += P_t V_j
+//                       (A = P_t from tensor memory, B = V_j MN-major). S_0, S_1,
+//                       O_0, O_1 are 128-column fp32 accumulators in TMEM.
+//   warps 10-11         idle; they only give their registers to the softmax groups
+//                       (setmaxnreg: 208 registers per softmax thread, 88 elsewhere).
 //
 // Issue order per key/value tile j:  S0_j, PV1_{j-1}, S1_j, PV0_j.  While one
 // softmax group works on its S, the tensor pipe runs the other tile's two MMAs.
@@ -33,6 +36,7 @@
 
 #include "attn_launch.h"
 #include "ptx.cuh"
+#include "softmax_row.cuh"
 
 #include <cuda_bf16.h>
 
@@ -56,20 +60,64 @@ constexpr float kLazyThreshold = 8.0f;  // log2 units
 #ifndef F2K_OPT_SETMAXNREG
 #define F2K_OPT_SETMAXNREG 1   // softmax warpgroups take registers from the load/MMA warpgroup
 #endif
-#ifndef F2K_OPT_PACKED
-#define F2K_OPT_PACKED 1       // f32x2 FMA/ADD and 3-input max in the softmax
+#ifndef F2K_OPT_P_PARTS
+#define F2K_OPT_P_PARTS 2      // P is handed to the MMA warp in this many parts (1, 2 or 4)
 #endif
-#ifndef F2K_OPT_SPLIT_P
-#define F2K_OPT_SPLIT_P 1      // hand P to the MMA warp in two 64-key halves
+#ifndef F2K_OPT_POLY_OF8
+#define F2K_OPT_POLY_OF8 0     // of every 8 key pairs, how many take 2^x on the FMA pipe (0..8)
 #endif
+constexpr int kPParts = F2K_OPT_P_PARTS;
 constexpr int kRegsSoftmax = 208, kRegsOther = 88;   // 2*128*208 + 128*88 = 64512 <= 384*168
+
+// Optional phase timing (bring-up builds only, -DF2K_PROFILE_PHASES): CTA (0,0,0) adds the SM
+// clock cycles each role spends per phase into the words after the status word.
+#ifdef F2K_PROFILE_PHASES
+#define PH_DECL long long ph_t = clock64()
+#define PH_MARK(slot)                                                                      \
+    do {                                                                                   \
+        const long long ph_n = clock64();                                                  \
+        if (ph_on) atomicAdd(reinterpret_cast<unsigned long long*>(p.status) + 1 + (slot), \
+                             (unsigned long long)(ph_n - ph_t));                           \
+        ph_t = ph_n;                                                                       \
+    } while (0)
+// like PH_MARK, and also counts the waits longer than 200 cycles (slot + 1) and keeps the longest (slot + 2)
+#define PH_MARK_HIST(slot)                                                                     \
+    do {                                                                                       \
+        const long long ph_n = clock64();                                                      \
+        if (ph_on) {                                                                           \
+            unsigned long long* b_ = reinterpret_cast<unsigned long long*>(p.status) + 1 + (slot); \
+            atomicAdd(b_, (unsigned long long)(ph_n - ph_t));                                  \
+            if (ph_n - ph_t > 200) atomicAdd(b_ + 1, 1ull);                                    \
+            atomicMax(b_ + 2, (unsigned long long)(ph_n - ph_t));                              \
+        }                                                                                      \
+        ph_t = ph_n;                                                                           \
+    } while (0)
+// raw event trace of CTA (0,0,0) for key tiles 8..11: every tracing thread owns a region of the
+// status buffer (plain stores, no atomics on the traced path)
+#define PH_EVDECL(base) int ph_ev = (base)
+#define PH_EVENT(id, jj)                                                                         \
+    do {                                                                                         \
+        if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (threadIdx.x & 31) == 0 &&  \
+            (jj) >= 8 && (jj) < 12) {                                                            \
+            reinterpret_cast<unsigned long long*>(p.status)[ph_ev++] =                           \
+                ((unsigned long long)(id) << 56) | ((unsigned long long)(jj) << 48) |            \
+                ((unsigned long long)clock64() & 0xFFFFFFFFFFFFull);                             \
+        }                                                                                        \
+    } while (0)
+#else
+#define PH_DECL
+#define PH_MARK(slot)
+#define PH_MARK_HIST(slot)
+#define PH_EVDECL(base)
+#define PH_EVENT(id, jj)
+#endif
 
 struct SmemCtl {
     uint64_t q_full[2];
     uint64_t kv_full[kStages];
     uint64_t kv_empty[kStages];
     uint64_t s_full[2];
-    uint64_t p_full[2][2];   // [tile][key half]
+    uint64_t p_full[2][kPParts];   // [tile][part of the key tile]
     uint64_t o_full[2];
     uint64_t drain;
     uint32_t tmem_base;
@@ -92,31 +140,35 @@ __device__ __forceinline__ void locate_tile(const int* tile_start, const int* le
     valid = min(kTileN, len[seg] - row0);
 }
 
-// S_t = Q_t K^T: 8 k-steps of 16 over head_dim; both operands K-major, 128-byte
-// swizzle, stored as two 128 x 64 boxes (k-steps 0-3 in the first, 4-7 in the second).
-__device__ __forceinline__ void issue_qk(uint32_t d_tmem, uint32_t q_smem, uint32_t k_smem) {
+// The MMA-issuing thread is a single lane that shares its scheduler with softmax warps, so every
+// instruction it needs per MMA delays the tensor pipe. Descriptors are therefore built once and
+// advanced by adding a compile-time constant to their low word (the start-address field counts
+// 16-byte units and never carries out of its 14 bits inside the CTA's shared memory).
+
+// S_t = Q_t K^T: 8 k-steps of 16 over head_dim; both operands K-major, 128-byte swizzle, stored as
+// two 128 x 64 boxes (k-steps 0-3 in the first, 4-7 in the second).
+__device__ __forceinline__ void issue_qk(uint32_t d_tmem, uint64_t q_desc, uint64_t k_desc) {
     constexpr uint32_t idesc = umma_idesc_bf16(kTileM, kTileN, /*b_mn_major=*/false);
 #pragma unroll
     for (int kk = 0; kk < kHeadDim / 16; ++kk) {
-        const uint32_t off = (kk >> 2) * kBoxBytes + (kk & 3) * 32;
-        umma_ss(d_tmem, umma_smem_desc(q_smem + off, 16, 1024),
-                umma_smem_desc(k_smem + off, 16, 1024), idesc, kk > 0 ? 1u : 0u);
+        constexpr uint32_t kBox16 = kBoxBytes >> 4;
+        const uint32_t off = (kk >> 2) * kBox16 + (kk & 3) * 2;   // in 16-byte units
+        umma_ss(d_tmem, q_desc + off, k_desc + off, idesc, kk > 0 ? 1u : 0u);
     }
 }
 
-// O_t (+)= P_t V: 8 k-steps of 16 keys. A = P_t in TMEM (two bf16 per 32-bit column,
-// 8 columns per k-step); B = V tile, MN-major: head_dim contiguous in 64-element
-// (128-byte) swizzled rows, one row per key, the second 64 head-dim elements one box
-// (16 KiB) further on; 8-key groups are 1024 bytes apart.
-// `half` selects k-steps 0-3 (keys 0-63) or 4-7 (keys 64-127).
-__device__ __forceinline__ void issue_pv_half(uint32_t d_tmem, uint32_t p_tmem, uint32_t v_smem,
-                                              int half, bool accumulate) {
+// O_t (+)= P_t V: 8 k-steps of 16 keys. A = P_t in TMEM (two bf16 per 32-bit column, 8 columns per
+// k-step); B = V tile, MN-major: head_dim contiguous in 64-element (128-byte) swizzled rows, one
+// row per key, the second 64 head-dim elements one box (16 KiB) further on; 8-key groups are
+// 1024 bytes apart. `part` selects 8 / kPParts consecutive k-steps.
+__device__ __forceinline__ void issue_pv_part(uint32_t d_tmem, uint32_t p_tmem, uint64_t v_desc,
+                                              int part, uint32_t accumulate) {
     constexpr uint32_t idesc = umma_idesc_bf16(kTileM, kHeadDim, /*b_mn_major=*/true);
+    constexpr int kSteps = 8 / kPParts;
 #pragma unroll
-    for (int k4 = 0; k4 < 4; ++k4) {
-        const int kk = half * 4 + k4;
-        umma_ts(d_tmem, p_tmem + kk * 8, umma_smem_desc(v_smem + kk * 2048, kBoxBytes, 1024),
-                idesc, (accumulate || kk > 0) ? 1u : 0u);
+    for (int k4 = 0; k4 < kSteps; ++k4) {
+        const int kk = part * kSteps + k4;
+        umma_ts(d_tmem, p_tmem + kk * 8, v_desc + kk * (2048 >> 4), idesc, kk > 0 ? 1u : accumulate);
     }
 }
 
@@ -141,8 +193,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ AttnParams p) {
         for (int i = 0; i < 2; ++i) {
             mbar_init(smem_u32(&ctl->q_full[i]), 1);
             mbar_init(smem_u32(&ctl->s_full[i]), 1);
-            mbar_init(smem_u32(&ctl->p_full[i][0]), 128);
-            mbar_init(smem_u32(&ctl->p_full[i][1]), 128);
+            for (int k = 0; k < kPParts; ++k) mbar_init(smem_u32(&ctl->p_full[i][k]), 128);
             mbar_init(smem_u32(&ctl->o_full[i]), 1);
         }
         for (int i = 0; i < kStages; ++i) {
@@ -173,6 +224,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ AttnParams p) {
             if (lane == 0) {
                 int issued = 0;
                 bool ok = true;
+                PH_EVDECL(300);
                 for (int t = 0; t < 2; ++t) {
                     const int qt = 2 * pair + t;
                     int seg, row0, valid;
@@ -195,20 +247,27 @@ attn_fwd_sm100_kernel(const __grid_constant__ AttnParams p) {
                     for (int kv = 0; kv < 2; ++kv) {
                         const int slot = issued % kStages;
                         const uint32_t par = (issued / kStages) & 1;
+                        PH_EVENT(1 + kv, j);   // loader: starts waiting for the slot of K_j (1) / V_j (2)
                         ok = mbar_wait(smem_u32(&ctl->kv_empty[slot]), par ^ 1u, abort_flag);
                         if (!ok) break;
+                        PH_EVENT(3 + kv, j);   // loader: slot free, copy issued
                         const uint32_t bar = smem_u32(&ctl->kv_full[slot]);
                         const uint32_t dst = smem + kSmemRing + slot * kTileBytes;
                         const CUtensorMap* tm = kv == 0 ? &p.tm_k[seg] : &p.tm_v[seg];
+#ifdef F2K_EXP_NOLOAD   // timing experiment only: no K/V traffic at all (results are garbage)
+                        (void)dst; (void)tm;
+                        mbar_arrive(bar);
+#else
                         mbar_arrive_expect_tx(bar, kTileBytes);
                         tma_load_4d(dst, tm, bar, 0, head, row0, bidx);
                         tma_load_4d(dst + kBoxBytes, tm, bar, 64, head, row0, bidx);
+#endif
                         ++issued;
                     }
                 }
                 if (!ok) {
                     // Leaving early: let the copies this thread started land first.
-                    const uint64_t lim = 20000000ull;  // 20 ms each, still bounded
+                    const long long lim = 40000000ll;  // ~20 ms each, still bounded
                     volatile uint32_t never = 0;
                     for (int t = 0; t < 2; ++t) mbar_wait(smem_u32(&ctl->q_full[t]), 0, &never, lim);
                     for (int i = max(0, issued - kStages); i < issued; ++i)
@@ -217,50 +276,79 @@ attn_fwd_sm100_kernel(const __grid_constant__ AttnParams p) {
             }
         } else if (warp == kMmaWarp) {
             // ------------------------------ MMA issuer --------------------------------
-            if (lane == 0) {
-                const uint32_t q0 = smem + kSmemQ, q1 = q0 + kTileBytes;
+            // The whole warp runs this loop converged; umma_* elect one lane per instruction.
+            {
                 bool ok = true;
+                // Descriptors: Q tiles (fixed for the CTA) and ring slot 0 as K (K-major) / V (MN-major).
+                const uint64_t q0_desc = umma_smem_desc(smem + kSmemQ, 16, 1024);
+                const uint64_t q1_desc = umma_smem_desc(smem + kSmemQ + kTileBytes, 16, 1024);
+                const uint64_t k_desc0 = umma_smem_desc(smem + kSmemRing, 16, 1024);
+                const uint64_t v_desc0 = umma_smem_desc(smem + kSmemRing, kBoxBytes, 1024);
+                const uint32_t bar_full0 = smem_u32(&ctl->kv_full[0]), bar_empty0 = smem_u32(&ctl->kv_empty[0]);
                 // Ring slot of K_j is 2j, of V_j is 2j+1.
-                auto slot_addr = [&](int n) { return smem + kSmemRing + (n % kStages) * kTileBytes; };
-                auto wait_full = [&](int n) {
-                    return mbar_wait(smem_u32(&ctl->kv_full[n % kStages]), (n / kStages) & 1, abort_flag);
+                auto slot_off16 = [&](int n) { return (uint32_t)(n % kStages) * (kTileBytes >> 4); };
+                auto wait_uniform = [&](uint32_t bar, uint32_t parity) {
+                    return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag)) != 0;
                 };
-                auto release = [&](int n) { umma_commit(smem_u32(&ctl->kv_empty[n % kStages])); };
-                // O_t (+)= P_t V_n, issued half by half as the softmax group hands P over.
+                auto wait_full = [&](int n) {
+                    return wait_uniform(bar_full0 + (n % kStages) * 8, (n / kStages) & 1);
+                };
+                auto release = [&](int n) { umma_commit(bar_empty0 + (n % kStages) * 8); };
+                // O_t (+)= P_t V_n, issued part by part as the softmax group hands P over.
                 auto issue_pv = [&](int t, int jj) -> bool {
                     const uint32_t d = tmem + (t == 0 ? kColO0 : kColO1);
                     const uint32_t a = tmem + (t == 0 ? kColS0 : kColS1);
+                    const uint64_t v_desc = v_desc0 + slot_off16(2 * jj + 1);
+                    const uint32_t bar_p = smem_u32(&ctl->p_full[t][0]);
 #pragma unroll
-                    for (int half = 0; half < 2; ++half) {
-                        if (!mbar_wait(smem_u32(&ctl->p_full[t][half]), jj & 1, abort_flag)) return false;
+                    for (int part = 0; part < kPParts; ++part) {
+                        if (!wait_uniform(bar_p + part * 8, jj & 1)) return false;
                         tc_fence_after_sync();
-                        issue_pv_half(d, a, slot_addr(2 * jj + 1), half, jj > 0);
+                        issue_pv_part(d, a, v_desc, part, jj > 0 ? 1u : 0u);
                     }
                     return true;
                 };
 
+#ifdef F2K_PROFILE_PHASES
+                const bool ph_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0;
+#endif
+                PH_DECL;
+                PH_EVDECL(64);
                 for (int j = 0; j < n_kv; ++j) {
                     // S0_j
+                    PH_EVENT(10, j);   // mma: starts waiting for K_j
                     if (!(ok = wait_full(2 * j))) break;
-                    if (j == 0 && !(ok = mbar_wait(smem_u32(&ctl->q_full[0]), 0, abort_flag))) break;
+                    PH_EVENT(11, j);   // mma: K_j there
+                    if (j == 0 && !(ok = wait_uniform(smem_u32(&ctl->q_full[0]), 0))) break;
+                    PH_MARK_HIST(24);   // waiting for K_j (+ count of long waits, longest)
                     tc_fence_after_sync();
-                    issue_qk(tmem + kColS0, q0, slot_addr(2 * j));
+                    issue_qk(tmem + kColS0, q0_desc, k_desc0 + slot_off16(2 * j));
                     umma_commit(smem_u32(&ctl->s_full[0]));
+                    PH_EVENT(12, j);   // mma: S0_j issued
+                    PH_MARK(17);   // issuing S0
                     // PV1_{j-1}
                     if (j > 0) {
                         if (!(ok = issue_pv(1, j - 1))) break;
                         release(2 * j - 1);
                     }
+                    PH_EVENT(13, j);   // mma: PV1_{j-1} issued, V_{j-1} released
+                    PH_MARK(18);   // waiting for P1 + issuing PV1
                     // S1_j
-                    if (j == 0 && !(ok = mbar_wait(smem_u32(&ctl->q_full[1]), 0, abort_flag))) break;
+                    if (j == 0 && !(ok = wait_uniform(smem_u32(&ctl->q_full[1]), 0))) break;
                     tc_fence_after_sync();
-                    issue_qk(tmem + kColS1, q1, slot_addr(2 * j));
+                    issue_qk(tmem + kColS1, q1_desc, k_desc0 + slot_off16(2 * j));
                     umma_commit(smem_u32(&ctl->s_full[1]));
                     release(2 * j);
+                    PH_EVENT(14, j);   // mma: S1_j issued, K_j released
+                    PH_MARK(19);   // issuing S1
                     // PV0_j
                     if (!(ok = wait_full(2 * j + 1))) break;
+                    PH_EVENT(15, j);   // mma: V_j there
+                    PH_MARK(20);   // waiting for V_j
                     if (!(ok = issue_pv(0, j))) break;
                     if (j == n_kv - 1) umma_commit(smem_u32(&ctl->o_full[0]));
+                    PH_EVENT(16, j);   // mma: PV0_j issued
+                    PH_MARK(21);   // waiting for P0 + issuing PV0
                 }
                 if (ok && n_kv > 0) {
                     // PV1 of the last tile
@@ -274,8 +362,9 @@ attn_fwd_sm100_kernel(const __grid_constant__ AttnParams p) {
                     // Leaving early: wait (bounded) until the MMAs already issued retire, so
                     // tensor memory is idle when it is freed.
                     volatile uint32_t never = 0;
+                    __syncwarp();
                     umma_commit(smem_u32(&ctl->drain));
-                    mbar_wait(smem_u32(&ctl->drain), 0, &never, 20000000ull);
+                    mbar_wait(smem_u32(&ctl->drain), 0, &never, 40000000ll);
                 }
             }
         }
@@ -294,6 +383,12 @@ attn_fwd_sm100_kernel(const __grid_constant__ AttnParams p) {
         float l_sum = 0.0f;
         bool ok = true;
 
+#ifdef F2K_PROFILE_PHASES
+        const bool ph_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (warp & 3) == 0 && lane == 0;
+        const int ph_base = t * 8;
+#endif
+        PH_DECL;
+        PH_EVDECL(160 + t * 64);
         int kv_seg = 0, kv_row0 = 0;
         for (int j = 0; j < n_kv; ++j) {
             const int valid = min(kTileN, p.kv_len[kv_seg] - kv_row0);
@@ -303,6 +398,8 @@ attn_fwd_sm100_kernel(const __grid_constant__ AttnParams p) {
             ok = mbar_wait(smem_u32(&ctl->s_full[t]), j & 1, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
+            if ((warp & 3) == 0) PH_EVENT(20 + t, j);   // softmax t: S_j seen
+            PH_MARK(ph_base + 0);   // waiting for S
             tc_fence_after_sync();
 
             uint32_t s[128];
@@ -317,31 +414,14 @@ attn_fwd_sm100_kernel(const __grid_constant__ AttnParams p) {
                 tmem_ld_x32(tS + 96, s3);
                 tmem_wait_ld();
             }
+            PH_MARK(ph_base + 1);   // S -> registers
             if (valid < kTileN) {  // last tile of a segment: keys past its end do not exist
 #pragma unroll
                 for (int i = 0; i < 128; ++i)
                     if (i >= valid) s[i] = __float_as_uint(-INFINITY);
             }
 
-            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
-#if F2K_OPT_PACKED
-#pragma unroll
-            for (int i = 0; i < 128; i += 8) {
-                mx0 = fmax3(mx0, __uint_as_float(s[i + 0]), __uint_as_float(s[i + 1]));
-                mx1 = fmax3(mx1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
-                mx2 = fmax3(mx2, __uint_as_float(s[i + 4]), __uint_as_float(s[i + 5]));
-                mx3 = fmax3(mx3, __uint_as_float(s[i + 6]), __uint_as_float(s[i + 7]));
-            }
-#else
-#pragma unroll
-            for (int i = 0; i < 128; i += 4) {
-                mx0 = fmaxf(mx0, __uint_as_float(s[i + 0]));
-                mx1 = fmaxf(mx1, __uint_as_float(s[i + 1]));
-                mx2 = fmaxf(mx2, __uint_as_float(s[i + 2]));
-                mx3 = fmaxf(mx3, __uint_as_float(s[i + 3]));
-            }
-#endif
-            const float m_tile = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+            const float m_tile = row_max128(s);
 
             const bool need = (m_tile - m_ref) * c > kLazyThreshold;
             if (__any_sync(0xffffffffu, need)) {
@@ -363,54 +443,26 @@ attn_fwd_sm100_kernel(const __grid_constant__ AttnParams p) {
                 }
             }
 
+            PH_MARK(ph_base + 2);   // row max, vote, (rare) rescale
             // P = 2^(c s - c m_ref), rounded to bf16 into the first 64 columns of S_t (two keys
             // per column); the row sum keeps the unrounded values.
             const float neg_mc = -m_ref * c;
-            float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
+            float sum[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
                 uint32_t pk[16];
-#pragma unroll
-                for (int i = 0; i < 32; i += 4) {
-                    float x0, x1, x2, x3;
-#if F2K_OPT_PACKED
-                    fma2(x0, x1, __uint_as_float(s[q * 32 + i + 0]), __uint_as_float(s[q * 32 + i + 1]),
-                         c, c, neg_mc, neg_mc);
-                    fma2(x2, x3, __uint_as_float(s[q * 32 + i + 2]), __uint_as_float(s[q * 32 + i + 3]),
-                         c, c, neg_mc, neg_mc);
-#else
-                    x0 = fmaf(__uint_as_float(s[q * 32 + i + 0]), c, neg_mc);
-                    x1 = fmaf(__uint_as_float(s[q * 32 + i + 1]), c, neg_mc);
-                    x2 = fmaf(__uint_as_float(s[q * 32 + i + 2]), c, neg_mc);
-                    x3 = fmaf(__uint_as_float(s[q * 32 + i + 3]), c, neg_mc);
-#endif
-                    const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
-                    const float p2 = ex2_approx(x2), p3 = ex2_approx(x3);
-#if F2K_OPT_PACKED
-                    add2(sum0, sum1, sum0, sum1, p0, p1);
-                    add2(sum2, sum3, sum2, sum3, p2, p3);
-#else
-                    sum0 += p0; sum1 += p1; sum2 += p2; sum3 += p3;
-#endif
-                    pk[i / 2 + 0] = pack_bf16x2(p0, p1);
-                    pk[i / 2 + 1] = pack_bf16x2(p2, p3);
-                }
+                exp_chunk32<F2K_OPT_POLY_OF8>(&s[q * 32], pk, c, neg_mc, sum);
                 tmem_st_x16(tS + q * 16, pk);
-#if F2K_OPT_SPLIT_P
-                if (q == 1 || q == 3) {   // keys 0-63, then keys 64-127, are ready for the MMA warp
+                if ((q + 1) % (4 / kPParts) == 0) {   // this part of the keys is ready for the MMA warp
+                    PH_MARK(ph_base + 3);   // exponentials
                     tmem_wait_st();
                     tc_fence_before_sync();
-                    mbar_arrive(smem_u32(&ctl->p_full[t][q >> 1]));
+                    mbar_arrive(smem_u32(&ctl->p_full[t][(q + 1) / (4 / kPParts) - 1]));
+                    if ((warp & 3) == 0) PH_EVENT(30 + t * 4 + (q + 1) / (4 / kPParts) - 1, j);   // softmax t: part handed over
+                    PH_MARK(ph_base + 4);   // store drain + hand-over
                 }
-#endif
             }
-#if !F2K_OPT_SPLIT_P
-            tmem_wait_st();
-            tc_fence_before_sync();
-            mbar_arrive(smem_u32(&ctl->p_full[t][0]));
-            mbar_arrive(smem_u32(&ctl->p_full[t][1]));
-#endif
-            l_sum += (sum0 + sum1) + (sum2 + sum3);
+            l_sum += (sum[0] + sum[1]) + (sum[2] + sum[3]);
         }
 
         // ------------------------------ epilogue ------------------------------------

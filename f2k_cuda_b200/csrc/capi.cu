@@ -19,6 +19,7 @@ namespace {
 using namespace f2k;
 
 constexpr size_t kAlign = 256;
+constexpr size_t kStatusBytes = 4096;   // the status word; bring-up builds keep phase counters behind it
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
@@ -194,9 +195,9 @@ int f2k_attn_create(const f2k_attn_config* cfg, f2k_attn** out) {
     if (e != cudaSuccess) return fail_cuda(h, "cudaDeviceGetAttribute", e);
     if (major != 10)
         return fail(h, F2K_ERR_UNSUPPORTED, "this library contains sm_100a code only (needs a B200-class GPU)");
-    e = cudaMalloc(reinterpret_cast<void**>(&h->d_status), sizeof(int));
+    e = cudaMalloc(reinterpret_cast<void**>(&h->d_status), kStatusBytes);
     if (e != cudaSuccess) return fail_cuda(h, "cudaMalloc(status)", e);
-    e = cudaMemset(h->d_status, 0, sizeof(int));
+    e = cudaMemset(h->d_status, 0, kStatusBytes);
     if (e != cudaSuccess) return fail_cuda(h, "cudaMemset(status)", e);
     h->valid = true;
     return F2K_OK;
@@ -423,5 +424,15 @@ int f2k_build_rope_4axis_tables(const int* axes_dim, int n_axes, const int* posi
 }
 
 const char* f2k_attn_version(void) { return "f2k_attn sm_100a 0.1"; }
+
+#ifdef F2K_PROFILE_PHASES
+// Bring-up builds only: copies the phase counters (64-bit words after the status word) out.
+int f2k_attn_debug_phases(f2k_attn* h, unsigned long long* out, int n) {
+    if (!h || !h->valid || n <= 0 || (size_t)(n + 1) * 8 > kStatusBytes) return F2K_ERR_INVALID;
+    if (cudaDeviceSynchronize() != cudaSuccess) return F2K_ERR_CUDA;
+    return cudaMemcpy(out, reinterpret_cast<unsigned long long*>(h->d_status) + 1, (size_t)n * 8,
+                      cudaMemcpyDeviceToHost) == cudaSuccess ? F2K_OK : F2K_ERR_CUDA;
+}
+#endif
 
 }  // extern "C"

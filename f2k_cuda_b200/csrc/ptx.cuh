@@ -15,12 +15,6 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
-__device__ __forceinline__ uint64_t global_timer_ns() {
-    uint64_t t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-
 __device__ __forceinline__ bool elect_one() {
     uint32_t pred = 0;
     asm volatile(
@@ -68,19 +62,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 
 // Bounded wait. `abort_flag` is a CTA-shared word any role sets when it gives up;
 // it is polled so that one expired wait releases every other waiter quickly.
-// Returns false when the limit (wall time on %globaltimer) ran out or the CTA is
-// aborting.
+// Returns false when the limit ran out or the CTA is aborting. The limit is kept on the
+// SM cycle counter and only looked at every 256 polls: the fast path is nothing but
+// try_wait (reading a timer on every miss would sit on the critical path of every
+// hand-over between the roles).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
                                           volatile uint32_t* abort_flag,
-                                          uint64_t limit_ns = 1000000000ull) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const uint64_t t0 = global_timer_ns();
-    uint32_t spins = 0;
-    while (true) {
+                                          long long limit_cycles = 2000000000ll) {
+    long long t0 = 0;
+    for (uint32_t spins = 1;; ++spins) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((++spins & 63u) == 0u) {
+        if ((spins & 255u) == 0u) {
             if (*abort_flag != 0u) return false;
-            if (global_timer_ns() - t0 > limit_ns) {
+            const long long now = clock64();
+            if (t0 == 0) {
+                t0 = now;
+            } else if (now - t0 > limit_cycles) {
                 *abort_flag = 1u;
                 return false;
             }
@@ -158,6 +155,20 @@ __device__ __forceinline__ void tmem_st_x32(uint32_t taddr, const uint32_t (&r)[
           "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
         : "memory");
 }
+// Narrow variants (8 columns) for rarely taken paths that must not cost registers.
+__device__ __forceinline__ void tmem_ld_x8(uint32_t taddr, uint32_t (&r)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+                   "=r"(r[7])
+                 : "r"(taddr)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_st_x8(uint32_t taddr, const uint32_t (&r)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]),
+                   "r"(r[6]), "r"(r[7])
+                 : "memory");
+}
 __device__ __forceinline__ void tmem_st_x16(uint32_t taddr, const uint32_t (&r)[16]) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
@@ -191,14 +202,19 @@ __host__ __device__ constexpr uint32_t umma_idesc_bf16(int m, int n, bool b_mn_m
            (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
 }
 
+// The issuing warp runs converged and every operand is warp-uniform; one elected lane issues.
+// (A divergent single-lane branch would force the operands out of the uniform datapath and cost
+// tens of cycles per MMA on a warp that shares its scheduler with the softmax warps.)
+
 // D[tmem] (+)= A[smem] * B[smem]
 __device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
                                         uint32_t idesc, uint32_t accumulate) {
     asm volatile(
         "{\n\t"
-        ".reg .pred p;\n\t"
+        ".reg .pred pe, p;\n\t"
+        "elect.sync _|pe, 0xffffffff;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
         "}\n"
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
@@ -208,18 +224,25 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
                                         uint32_t idesc, uint32_t accumulate) {
     asm volatile(
         "{\n\t"
-        ".reg .pred p;\n\t"
+        ".reg .pred pe, p;\n\t"
+        "elect.sync _|pe, 0xffffffff;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
         "}\n"
         ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
-// Arrive (count 1) on `bar` once every tcgen05 operation this thread issued before
-// the commit has completed.
+// Arrive (count 1) on `bar` once every tcgen05 operation the elected lane issued before the
+// commit has completed. elect.sync picks the same lane every time for a full warp, so the
+// commit tracks the MMAs issued through umma_ss / umma_ts.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
-                 ::"r"(bar) : "memory");
+    asm volatile(
+        "{\n\t"
+        ".reg .pred pe;\n\t"
+        "elect.sync _|pe, 0xffffffff;\n\t"
+        "@pe tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t"
+        "}\n"
+        ::"r"(bar) : "memory");
 }
 
 // ----------------------------------------------------------------------------
@@ -268,6 +291,25 @@ __device__ __forceinline__ void add2(float& d0, float& d1, float a0, float a1, f
         : "=f"(d0), "=f"(d1)
         : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
 }
+// 2^x for a pair of arguments on the FMA pipe instead of the special-function unit:
+// round-to-nearest split x = n + f with the 1.5*2^23 trick, cubic fit of 2^f on [-0.5, 0.5]
+// (relative error < 1e-4, far inside bf16 resolution), exponent patched in with one integer
+// multiply-add. Arguments are clamped at -126 (result flushes towards 0 below that).
+__device__ __forceinline__ void ex2_poly2(float& r0, float& r1, float x0, float x1) {
+    constexpr float kMagic = 12582912.0f;  // 1.5 * 2^23
+    x0 = fmaxf(x0, -126.0f);
+    x1 = fmaxf(x1, -126.0f);
+    float t0, t1, n0, n1, f0, f1, p0, p1;
+    add2(t0, t1, x0, x1, kMagic, kMagic);
+    add2(n0, n1, t0, t1, -kMagic, -kMagic);
+    fma2(f0, f1, n0, n1, -1.0f, -1.0f, x0, x1);
+    fma2(p0, p1, f0, f1, 0.0550886838f, 0.0550886838f, 0.242604051f, 0.242604051f);
+    fma2(p0, p1, p0, p1, f0, f1, 0.693276242f, 0.693276242f);
+    fma2(p0, p1, p0, p1, f0, f1, 0.99992894f, 0.99992894f);
+    r0 = __uint_as_float(__float_as_uint(t0) * (1u << 23) + __float_as_uint(p0));
+    r1 = __uint_as_float(__float_as_uint(t1) * (1u << 23) + __float_as_uint(p1));
+}
+
 __device__ __forceinline__ float ex2_approx(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));

@@ -1,0 +1,77 @@
+// Per-row softmax arithmetic of the attention kernel: a thread owns one query row of a
+// 128-key tile in registers (fp32 scores as loaded from tensor memory).
+//
+//   row_max128      maximum of the 128 scores
+//   exp_chunk32     P = 2^(c*s + neg_mc) for 32 scores -> 16 packed bf16 pairs, and the sum of
+//                   the unrounded values (four partial sums)
+//
+// 2^x comes from two places so that neither pipe is the bottleneck: the special-function
+// unit (ex2.approx, 4 lanes per clock per scheduler) and a cubic polynomial on the FMA pipe
+// (`kPolyOf8` of every 8 key pairs). Both agree to better than 1e-4 relative, far inside the
+// bf16 rounding P goes through next.
+#pragma once
+
+#include "ptx.cuh"
+
+namespace f2k {
+
+__device__ __forceinline__ float row_max128(const uint32_t (&s)[128]) {
+    using namespace f2k::ptx;
+    float m[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+        m[k] = fmaxf(__uint_as_float(s[2 * k]), __uint_as_float(s[2 * k + 1]));
+#pragma unroll
+    for (int i = 16; i < 128; i += 16)
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+            m[k] = fmax3(m[k], __uint_as_float(s[i + 2 * k]), __uint_as_float(s[i + 2 * k + 1]));
+    return fmaxf(fmax3(m[0], m[1], m[2]), fmax3(fmax3(m[3], m[4], m[5]), m[6], m[7]));
+}
+
+// 2^x for a pair on the FMA pipe. x = n + f by the 1.5*2^23 rounding trick, cubic fit of 2^f on
+// [-0.5, 0.5], exponent patched in with an integer shift-add. x is clamped at -126 so that the
+// exponent arithmetic cannot wrap (the result is then ~2^-126, i.e. nothing).
+__device__ __forceinline__ void exp2_fma_pair(float& r0, float& r1, float x0, float x1) {
+    using namespace f2k::ptx;
+    constexpr float kMagic = 12582912.0f;  // 1.5 * 2^23
+    x0 = fmaxf(x0, -126.0f);
+    x1 = fmaxf(x1, -126.0f);
+    float t0, t1, n0, n1, f0, f1, p0, p1;
+    add2(t0, t1, x0, x1, kMagic, kMagic);
+    add2(n0, n1, t0, t1, -kMagic, -kMagic);
+    add2(f0, f1, x0, x1, -n0, -n1);
+    fma2(p0, p1, f0, f1, 0.0550886838f, 0.0550886838f, 0.242604051f, 0.242604051f);
+    fma2(p0, p1, p0, p1, f0, f1, 0.693276242f, 0.693276242f);
+    fma2(p0, p1, p0, p1, f0, f1, 0.99992894f, 0.99992894f);
+    r0 = __uint_as_float((__float_as_uint(t0) << 23) + __float_as_uint(p0));
+    r1 = __uint_as_float((__float_as_uint(t1) << 23) + __float_as_uint(p1));
+}
+
+template <int kPolyOf8>
+__device__ __forceinline__ void exp_chunk32(const uint32_t* s, uint32_t (&pk)[16], float c,
+                                            float neg_mc, float (&sum)[4]) {
+    using namespace f2k::ptx;
+#pragma unroll
+    for (int i = 0; i < 32; i += 4) {
+        float x0, x1, x2, x3;
+        fma2(x0, x1, __uint_as_float(s[i + 0]), __uint_as_float(s[i + 1]), c, c, neg_mc, neg_mc);
+        fma2(x2, x3, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]), c, c, neg_mc, neg_mc);
+        // pair index within a group of 8 pairs (16 keys); the polynomial pairs are spread out
+        // so that both pipes stay busy all the way through the chunk
+        const int pa = (i >> 1) & 7, pb = pa + 1;
+        const bool poly_a = ((pa + 1) * kPolyOf8 / 8) != (pa * kPolyOf8 / 8);
+        const bool poly_b = ((pb + 1) * kPolyOf8 / 8) != (pb * kPolyOf8 / 8);
+        float p0, p1, p2, p3;
+        if (poly_a) exp2_fma_pair(p0, p1, x0, x1);
+        else { p0 = ex2_approx(x0); p1 = ex2_approx(x1); }
+        if (poly_b) exp2_fma_pair(p2, p3, x2, x3);
+        else { p2 = ex2_approx(x2); p3 = ex2_approx(x3); }
+        add2(sum[0], sum[1], sum[0], sum[1], p0, p1);
+        add2(sum[2], sum[3], sum[2], sum[3], p2, p3);
+        pk[i / 2 + 0] = pack_bf16x2(p0, p1);
+        pk[i / 2 + 1] = pack_bf16x2(p2, p3);
+    }
+}
+
+}  // namespace f2k
