@@ -46,6 +46,14 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
     v.w = pack2(f[6], f[7]);
     return v;
 }
+// One rotation, with the roundings spelled out: x0 c - x1 s as fma(x0, c, -(x1 s)) and
+// x0 s + x1 c as fma(x1, c, x0 s). This is what nvcc makes of the reference kernel's expressions
+// (src/backend/cuda/kernels/rope_4axis.cu:35-36), so the stand-alone kernels reproduce its bits.
+__device__ __forceinline__ void rotate_pair(float& y0, float& y1, float x0, float x1, float c, float s) {
+    y0 = __fmaf_rn(x0, c, -__fmul_rn(x1, s));
+    y1 = __fmaf_rn(x1, c, __fmul_rn(x0, s));
+}
+
 // Sum over the 16 lanes of a half-warp (xor offsets below 16 never leave the half).
 // The two halves of a warp may leave the row loop at different times, so each half
 // synchronises only with itself.
@@ -109,8 +117,7 @@ qk_prologue_kernel(const __grid_constant__ QkPrologueParams p) {
         for (int k = 0; k < 4; ++k) {
             const float a = v[2 * k] * rrms * g[2 * k];
             const float b = v[2 * k + 1] * rrms * g[2 * k + 1];
-            y[2 * k]     = a * cs[k] - b * sn[k];
-            y[2 * k + 1] = a * sn[k] + b * cs[k];
+            rotate_pair(y[2 * k], y[2 * k + 1], a, b, cs[k], sn[k]);
         }
         reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(job.y) + lr * kHeadDim)[hl] = pack8(y);
     }
@@ -199,10 +206,7 @@ rope4_rows128_kernel(__nv_bfloat16* __restrict__ x, const float* __restrict__ co
         const float cs[4] = {c4.x, c4.y, c4.z, c4.w};
         const float sn[4] = {s4.x, s4.y, s4.z, s4.w};
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            o[2 * k]     = v[2 * k] * cs[k] - v[2 * k + 1] * sn[k];
-            o[2 * k + 1] = v[2 * k] * sn[k] + v[2 * k + 1] * cs[k];
-        }
+        for (int k = 0; k < 4; ++k) rotate_pair(o[2 * k], o[2 * k + 1], v[2 * k], v[2 * k + 1], cs[k], sn[k]);
         *xp = pack8(o);
     }
 }
@@ -226,7 +230,9 @@ rope4_rows_generic_kernel(__nv_bfloat16* __restrict__ x, const float* __restrict
             const float x0 = __uint_as_float(w << 16);
             const float x1 = __uint_as_float(w & 0xFFFF0000u);
             const float c = __ldg(cr + k), s = __ldg(sr + k);
-            xr[k] = pack2(x0 * c - x1 * s, x0 * s + x1 * c);
+            float y0, y1;
+            rotate_pair(y0, y1, x0, x1, c, s);
+            xr[k] = pack2(y0, y1);
         }
     }
 }

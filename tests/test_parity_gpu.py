@@ -187,12 +187,8 @@ def test_rope_kernel(f2k, orc, seq, H, D):
     assert f2k.rope_4axis_inplace_bf16(dx, torch.from_numpy(cos).cuda(), torch.from_numpy(sin).cuda(),
                                        torch.from_numpy(pos_ids).cuda(), seq * H, D, seq)
     torch.cuda.synchronize()
-    # Same rounding points as the oracle's statement of the reference kernel; the compilers may
-    # fuse x0*c - x1*s differently, which can flip the last bf16 bit of a few elements per million.
-    from f2k_cuda_b200.inputs import from_bf16_bits
-    got, ref = host_bits(dx), orc.rope_bf16(x, cos, sin, pos_ids, seq)
-    assert np.mean(got != ref) < 1e-4
-    assert np.max(np.abs(from_bf16_bits(got) - from_bf16_bits(ref))) <= 2.0 ** -5
+    # bit for bit: kernel and oracle spell out the same fused multiply-adds
+    assert np.array_equal(host_bits(dx), orc.rope_bf16(x, cos, sin, pos_ids, seq))
 
 
 def test_against_the_reference_kernels_on_this_gpu(f2k, reflib):
