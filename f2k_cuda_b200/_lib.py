@@ -37,6 +37,8 @@ def _declare(lib: C.CDLL) -> None:
     lib.f2k_attn_forward_fused.argtypes = [vp] * 15 + [f, vp, vp, vp, sz, vp]
     lib.f2k_attn_forward_fused_host.restype = i
     lib.f2k_attn_forward_fused_host.argtypes = [vp] * 15 + [f, vp, vp, vp]
+    lib.f2k_attn_forward_fused_noalloc.restype = i
+    lib.f2k_attn_forward_fused_noalloc.argtypes = [C.POINTER(AttnConfig)] + [vp] * 14 + [f, vp, vp, vp, C.c_char_p, sz]
     lib.f2k_attn_device_status.restype = i
     lib.f2k_attn_device_status.argtypes = [vp, C.POINTER(i)]
     lib.f2k_rmsnorm_bf16.restype = i
@@ -56,7 +58,19 @@ def load(path: Path | None = None) -> C.CDLL:
     if not path.exists():
         raise ImportError(f"{path} is missing and could not be built; f2k_cuda_b200 has no fallback path")
     lib = C.CDLL(str(path))
-    _declare(lib)
+    try:
+        _declare(lib)
+    except AttributeError:
+        # a library from an older source tree: rebuild it once and bind the fresh file
+        if path != LIB_PATH:
+            raise
+        build(force=True)
+        import shutil
+        import tempfile
+        fresh = Path(tempfile.mkdtemp(prefix="f2k_attn_")) / path.name   # dlopen caches by path
+        shutil.copy2(path, fresh)
+        lib = C.CDLL(str(fresh))
+        _declare(lib)
     return lib
 
 

@@ -118,6 +118,29 @@ int f2k_attn_forward_fused_host(f2k_attn* h,
                                 float eps,
                                 void* ho_txt, void* ho_img, void* stream);
 
+/* The computation of f2k_attn_forward_fused for callers that cannot allocate device memory:
+ * a real-time loop that may not take the allocator's locks, a plug-in whose host application
+ * forbids device allocations after start-up, a process whose device memory was all handed out
+ * at start-up. It
+ * needs no handle (f2k_attn_create allocates a status word) and no workspace: both live in a
+ * 32 MiB array that is part of the library image on every GPU that loads it. Shapes whose
+ * normalised Q and K copies do not fit (256 + 2*B*(seq_txt+seq_img)*n_heads*128*2 bytes, each
+ * tensor rounded up to 256) are refused with F2K_ERR_WORKSPACE and a message.
+ * The first call on a device looks the array's device address up; make that call before any
+ * stream capture starts. Nothing in the call allocates or frees. All calls on a device share
+ * the array: calls whose GPU work may overlap race on it, so keep them on one stream.
+ * errbuf (may be NULL) receives a message when the result is not F2K_OK.
+ * No counterpart in the reference, whose callers always allocate their own workspace. */
+int f2k_attn_forward_fused_noalloc(const f2k_attn_config* cfg,
+                                   const void* q_txt, const void* k_txt, const void* v_txt,
+                                   const void* q_img, const void* k_img, const void* v_img,
+                                   const void* gamma_q_txt, const void* gamma_k_txt,
+                                   const void* gamma_q_img, const void* gamma_k_img,
+                                   const float* cos_txt, const float* sin_txt,
+                                   const float* cos_img, const float* sin_img,
+                                   float eps, void* o_txt, void* o_img, void* stream,
+                                   char* errbuf, size_t errbuf_len);
+
 /* Reads and clears the device status word the kernels of this handle write
  * (0 = clean). Synchronises the device. A non-zero word means a bounded wait inside
  * a kernel expired and the last outputs must not be used; the call then returns
