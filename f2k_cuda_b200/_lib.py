@@ -13,6 +13,12 @@ from .build import LIB_PATH, build
 F2K_OK, F2K_ERR_INVALID, F2K_ERR_UNSUPPORTED, F2K_ERR_WORKSPACE, F2K_ERR_CUDA, F2K_ERR_DEVICE = range(6)
 
 
+class SeqParConfig(C.Structure):
+    """struct f2k_seqpar_config"""
+    _fields_ = [("batch", C.c_int), ("seq_local", C.c_int), ("n_heads", C.c_int), ("head_dim", C.c_int),
+                ("world", C.c_int), ("rank", C.c_int), ("scale", C.c_float)]
+
+
 class AttnConfig(C.Structure):
     """struct f2k_attn_config"""
     _fields_ = [("batch", C.c_int), ("seq_txt", C.c_int), ("seq_img", C.c_int),
@@ -47,6 +53,30 @@ def _declare(lib: C.CDLL) -> None:
     lib.f2k_rope_4axis_inplace_bf16.argtypes = [vp, vp, vp, vp, i, i, i, vp]
     lib.f2k_build_rope_4axis_tables.restype = i
     lib.f2k_build_rope_4axis_tables.argtypes = [vp, i, vp, i, f, vp, vp]
+    lib.f2k_seqpar_create.restype = i
+    lib.f2k_seqpar_create.argtypes = [C.POINTER(SeqParConfig), C.POINTER(vp)]
+    lib.f2k_seqpar_destroy.restype = None
+    lib.f2k_seqpar_destroy.argtypes = [vp]
+    lib.f2k_seqpar_last_error.restype = C.c_char_p
+    lib.f2k_seqpar_last_error.argtypes = [vp]
+    lib.f2k_seqpar_buffer.restype = i
+    lib.f2k_seqpar_buffer.argtypes = [vp, C.POINTER(vp), C.POINTER(sz)]
+    lib.f2k_seqpar_attach.restype = i
+    lib.f2k_seqpar_attach.argtypes = [vp, C.POINTER(vp)]
+    lib.f2k_seqpar_local_kv.restype = i
+    lib.f2k_seqpar_local_kv.argtypes = [vp, C.POINTER(vp), C.POINTER(vp)]
+    lib.f2k_seqpar_forward.restype = i
+    lib.f2k_seqpar_forward.argtypes = [vp, vp, vp, i, vp, vp]
+    lib.f2k_seqpar_device_status.restype = i
+    lib.f2k_seqpar_device_status.argtypes = [vp, C.POINTER(i)]
+    lib.f2k_ipc_export.restype = i
+    lib.f2k_ipc_export.argtypes = [vp, vp]
+    lib.f2k_ipc_open.restype = i
+    lib.f2k_ipc_open.argtypes = [vp, C.POINTER(vp)]
+    lib.f2k_ipc_close.restype = i
+    lib.f2k_ipc_close.argtypes = [vp]
+    lib.f2k_qk_norm_rope_bf16.restype = i
+    lib.f2k_qk_norm_rope_bf16.argtypes = [vp, vp, vp, vp, vp, i, i, i, f, vp]
     lib.f2k_attn_version.restype = C.c_char_p
     lib.f2k_attn_version.argtypes = []
 

@@ -48,7 +48,7 @@ class _Module:
 
     def __del__(self):
         h, self._h = getattr(self, "_h", None), None
-        if h:
+        if h and lib is not None:
             lib.f2k_attn_destroy(h)
 
     def ok(self) -> bool:

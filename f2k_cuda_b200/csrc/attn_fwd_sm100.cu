@@ -243,7 +243,14 @@ attn_fwd_sm100_kernel(const __grid_constant__ AttnParams p) {
                 for (int j = 0; j < n_kv && ok; ++j) {
                     int seg, row0, valid;
                     locate_tile<kMaxKvSeg>(p.kv_tile_start, p.kv_len, p.n_kvseg, j, seg, row0, valid);
-    #pragma unroll
+                    if (row0 == 0 && p.kv_ready[seg] != nullptr) {
+                        // first tile of a segment that is being copied in: wait for its arrival word,
+                        // then order the copy engine's writes before this thread's TMA reads
+                        ok = global_flag_wait(p.kv_ready[seg], p.kv_ready_value, abort_flag);
+                        if (!ok) break;
+                        asm volatile("fence.proxy.async.global;" ::: "memory");
+                    }
+#pragma unroll
                     for (int kv = 0; kv < 2; ++kv) {
                         const int slot = issued % kStages;
                         const uint32_t par = (issued / kStages) & 1;

@@ -52,6 +52,14 @@ struct AttnParams {
     float scale_log2;                 // softmax scale * log2(e)
 
     int* status;                      // device word, AttnStatus bits OR-ed in
+
+    // Sequence-parallel use: key/value segment i may still be on its way into this GPU's memory
+    // when the kernel starts (a copy engine is bringing it over NVLink). When kv_ready[i] is not
+    // null the TMA producer waits, bounded, until that word equals kv_ready_value before it
+    // touches the segment. The word is written after the copy, in stream order, by the copying
+    // stream. Null for data that is already in place.
+    const unsigned int* kv_ready[kMaxKvSeg];
+    unsigned int        kv_ready_value;
 };
 
 }  // namespace f2k

@@ -85,6 +85,30 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
     }
 }
 
+// Bounded wait on a word in global memory that another engine of this GPU (a copy engine, a
+// stream memory operation) sets to `value`. Same contract as mbar_wait.
+__device__ __forceinline__ bool global_flag_wait(const unsigned int* flag, unsigned int value,
+                                                 volatile uint32_t* abort_flag,
+                                                 long long limit_cycles = 2000000000ll) {
+    long long t0 = 0;
+    for (uint32_t spins = 1;; ++spins) {
+        unsigned int v;
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+        if (v == value) return true;
+        if ((spins & 63u) == 0u) {
+            if (*abort_flag != 0u) return false;
+            const long long now = clock64();
+            if (t0 == 0) {
+                t0 = now;
+            } else if (now - t0 > limit_cycles) {
+                *abort_flag = 1u;
+                return false;
+            }
+        }
+        __nanosleep(200);
+    }
+}
+
 // ----------------------------------------------------------------------------
 // TMA (tiled, 4-D, global -> shared, completion on an mbarrier). No multicast.
 // ----------------------------------------------------------------------------

@@ -1,0 +1,301 @@
+// Sequence-parallel ("ring") joint attention across the GPUs of one NVLink/NVSwitch box, and the
+// stand-alone entry point of the QK prologue kernel it uses.
+//
+// The reference has no multi-GPU code at all (one process, one GPU, batch 1); this layer is new.
+// Tokens are sharded by rank: rank r holds Q, K, V of its `seq_local` tokens. Every rank needs
+// every other rank's K and V. Each rank owns ONE device allocation:
+//
+//     [2 sets][world slots] K shards | [2 sets][world slots] V shards | [2 sets][world] arrival words
+//
+// A rank writes its own normalised K and its V into slot `rank` of the current set (the set
+// alternates from call to call). After a cross-rank barrier (the host's job: every rank's slot
+// is written), forward() pulls slot p of rank p's allocation into slot p of the local one for
+// every other rank p, in ring order rank+1, rank+2, ..., with the COPY ENGINES
+// (cudaMemcpyAsync through a peer mapping, no SMs), and after each pull writes the arrival word
+// of that slot with a stream memory operation. The attention kernel is launched at once on the
+// compute stream with one key/value segment per rank: its own first, then the others in the
+// order they arrive; its TMA producer waits (bounded) on a segment's arrival word before the
+// first tile of that segment. So the transfer of shard i+1 overlaps the MMAs on shard i, remote
+// data is only ever read from local memory by ordinary non-multicast TMA, and nothing waits on
+// another kernel. With overlap off the compute stream simply waits for all pulls.
+//
+// Two sets: a rank may start writing the next call's K/V while slower peers still pull the
+// current set. The barrier of call n+1 comes after every rank's attention kernel of call n (in
+// stream order), and that kernel cannot finish before its pulls have landed, so set n is free
+// again when call n+2 writes it.
+
+#include "f2k_attn.h"
+
+#include "attn_launch.h"
+
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <string>
+#include <vector>
+
+namespace {
+using namespace f2k;
+constexpr size_t kAlign = 256;
+inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                   CUtensorMapFloatOOBfill);
+using WriteValue32Fn = CUresult (*)(CUstream, CUdeviceptr, cuuint32_t, unsigned int);
+
+void* driver_fn(const char* name) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint(name, &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+        return nullptr;
+    return p;
+}
+}  // namespace
+
+struct f2k_seqpar {
+    f2k_seqpar_config cfg{};
+    float  scale = 0.f;
+    bool   valid = false;
+    std::string err;
+    unsigned char* buf = nullptr;       // the allocation described above
+    size_t shard_bytes = 0, set_bytes = 0, total_bytes = 0, flags_off = 0;
+    int*   d_status = nullptr;
+    std::vector<unsigned char*> peer;   // base of every rank's allocation as mapped here
+    unsigned int epoch = 0;             // call counter; arrival words carry it
+    cudaEvent_t pulled = nullptr;
+    EncodeTiledFn  encode = nullptr;
+    WriteValue32Fn write32 = nullptr;
+
+    unsigned char* k_slot(unsigned char* base, int set, int slot) const {
+        return base + ((size_t)set * cfg.world + slot) * shard_bytes;
+    }
+    unsigned char* v_slot(unsigned char* base, int set, int slot) const {
+        return base + 2 * set_bytes + ((size_t)set * cfg.world + slot) * shard_bytes;
+    }
+    unsigned int* flag(int set, int slot) const {
+        return reinterpret_cast<unsigned int*>(buf + flags_off) + set * cfg.world + slot;
+    }
+};
+
+namespace {
+int fail(f2k_seqpar* h, int code, std::string msg) {
+    h->err = std::move(msg);
+    return code;
+}
+int fail_cuda(f2k_seqpar* h, const char* what, cudaError_t e) {
+    return fail(h, F2K_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
+}
+bool encode(f2k_seqpar* h, CUtensorMap* map, const void* base, int len) {
+    const f2k_seqpar_config& c = h->cfg;
+    const cuuint64_t tok = (cuuint64_t)c.n_heads * kHeadDim;
+    const cuuint64_t dims[4]    = {(cuuint64_t)kHeadDim, (cuuint64_t)c.n_heads, (cuuint64_t)len, (cuuint64_t)c.batch};
+    const cuuint64_t strides[3] = {(cuuint64_t)kHeadDim * 2, tok * 2, tok * (cuuint64_t)len * 2};
+    const cuuint32_t box[4]     = {64, 1, (cuuint32_t)kTileM, 1};
+    const cuuint32_t estr[4]    = {1, 1, 1, 1};
+    return h->encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+}  // namespace
+
+extern "C" {
+
+int f2k_seqpar_create(const f2k_seqpar_config* cfg, f2k_seqpar** out) {
+    if (!out) return F2K_ERR_INVALID;
+    *out = nullptr;
+    f2k_seqpar* h = new (std::nothrow) f2k_seqpar();
+    if (!h) return F2K_ERR_CUDA;
+    *out = h;
+    if (!cfg) return fail(h, F2K_ERR_INVALID, "null config");
+    h->cfg = *cfg;
+    if (cfg->batch <= 0 || cfg->seq_local <= 0 || cfg->n_heads <= 0 || cfg->head_dim <= 0)
+        return fail(h, F2K_ERR_INVALID, "sequence-parallel attention: zero/negative dim");
+    if (cfg->world <= 0 || cfg->world > kMaxKvSeg || cfg->rank < 0 || cfg->rank >= cfg->world)
+        return fail(h, F2K_ERR_INVALID, "sequence-parallel attention: world must be 1..8 and 0 <= rank < world");
+    if (cfg->head_dim != kHeadDim) return fail(h, F2K_ERR_UNSUPPORTED, "head_dim must be 128");
+    h->scale = cfg->scale > 0.f ? cfg->scale : 1.0f / std::sqrt((float)cfg->head_dim);
+    h->shard_bytes = align_up((size_t)cfg->batch * cfg->seq_local * cfg->n_heads * kHeadDim * 2, kAlign);
+    h->set_bytes   = (size_t)cfg->world * h->shard_bytes;
+    h->flags_off   = 4 * h->set_bytes;
+    h->total_bytes = h->flags_off + align_up((size_t)2 * cfg->world * sizeof(unsigned int), kAlign);
+
+    int dev = 0, major = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail_cuda(h, "cudaGetDevice", e);
+    e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+    if (e != cudaSuccess) return fail_cuda(h, "cudaDeviceGetAttribute", e);
+    if (major != 10) return fail(h, F2K_ERR_UNSUPPORTED, "this library contains sm_100a code only");
+    h->encode  = reinterpret_cast<EncodeTiledFn>(driver_fn("cuTensorMapEncodeTiled"));
+    h->write32 = reinterpret_cast<WriteValue32Fn>(driver_fn("cuStreamWriteValue32"));
+    if (!h->encode || !h->write32) return fail(h, F2K_ERR_CUDA, "driver entry points unavailable");
+    e = cudaMalloc(reinterpret_cast<void**>(&h->buf), h->total_bytes);
+    if (e != cudaSuccess) return fail_cuda(h, "cudaMalloc(shards)", e);
+    e = cudaMemset(h->buf + h->flags_off, 0, h->total_bytes - h->flags_off);
+    if (e != cudaSuccess) return fail_cuda(h, "cudaMemset(flags)", e);
+    e = cudaMalloc(reinterpret_cast<void**>(&h->d_status), 256);
+    if (e == cudaSuccess) e = cudaMemset(h->d_status, 0, 256);
+    if (e != cudaSuccess) return fail_cuda(h, "cudaMalloc(status)", e);
+    e = cudaEventCreateWithFlags(&h->pulled, cudaEventDisableTiming);
+    if (e != cudaSuccess) return fail_cuda(h, "cudaEventCreate", e);
+    h->peer.assign(cfg->world, nullptr);
+    h->peer[cfg->rank] = h->buf;
+    h->valid = true;
+    return F2K_OK;
+}
+
+void f2k_seqpar_destroy(f2k_seqpar* h) {
+    if (!h) return;
+    if (h->pulled) cudaEventDestroy(h->pulled);
+    if (h->d_status) cudaFree(h->d_status);
+    if (h->buf) cudaFree(h->buf);
+    delete h;
+}
+
+const char* f2k_seqpar_last_error(const f2k_seqpar* h) { return h ? h->err.c_str() : "no handle"; }
+
+int f2k_seqpar_buffer(f2k_seqpar* h, void** base, size_t* bytes) {
+    if (!h || !h->valid) return F2K_ERR_INVALID;
+    if (base) *base = h->buf;
+    if (bytes) *bytes = h->total_bytes;
+    return F2K_OK;
+}
+
+int f2k_seqpar_attach(f2k_seqpar* h, void* const* peer_bases) {
+    if (!h || !h->valid || !peer_bases) return F2K_ERR_INVALID;
+    for (int r = 0; r < h->cfg.world; ++r) {
+        if (r == h->cfg.rank) continue;
+        if (!peer_bases[r]) return fail(h, F2K_ERR_INVALID, "null peer buffer");
+        h->peer[r] = static_cast<unsigned char*>(peer_bases[r]);
+    }
+    return F2K_OK;
+}
+
+int f2k_seqpar_local_kv(f2k_seqpar* h, void** k, void** v) {
+    if (!h || !h->valid) return F2K_ERR_INVALID;
+    const int set = (h->epoch + 1) & 1;   // the set the NEXT forward call reads
+    if (k) *k = h->k_slot(h->buf, set, h->cfg.rank);
+    if (v) *v = h->v_slot(h->buf, set, h->cfg.rank);
+    return F2K_OK;
+}
+
+int f2k_seqpar_forward(f2k_seqpar* h, const void* q_local, void* o_local, int overlap,
+                       void* compute_stream, void* copy_stream) {
+    if (!h || !h->valid) return F2K_ERR_INVALID;
+    if (!q_local || !o_local) return fail(h, F2K_ERR_INVALID, "null tensor pointer");
+    const f2k_seqpar_config& c = h->cfg;
+    for (int r = 0; r < c.world; ++r)
+        if (!h->peer[r]) return fail(h, F2K_ERR_INVALID, "peers not attached");
+    h->epoch += 1;
+    const int set = h->epoch & 1;
+    cudaStream_t cs = static_cast<cudaStream_t>(compute_stream);
+    cudaStream_t ps = static_cast<cudaStream_t>(copy_stream);
+    if (c.world > 1 && ps == cs && overlap)
+        return fail(h, F2K_ERR_INVALID, "overlap needs a copy stream different from the compute stream");
+
+    AttnParams p;
+    std::memset(&p, 0, sizeof p);
+    const long long tok = (long long)c.n_heads * kHeadDim;
+    if (!encode(h, &p.tm_q[0], q_local, c.seq_local)) return fail(h, F2K_ERR_CUDA, "tensor map (Q) failed");
+    p.o_ptr[0] = o_local;
+    p.o_tok_stride[0] = tok;
+    p.o_batch_stride[0] = tok * c.seq_local;
+    p.q_len[0] = c.seq_local;
+    const int tiles_per_seg = (c.seq_local + kTileM - 1) / kTileM;
+    p.q_tile_start[0] = 0;
+    p.q_tile_start[1] = tiles_per_seg;
+    p.n_qseg = 1;
+    p.n_q_tiles = tiles_per_seg;
+
+    // pulls in ring order; key/value segment i of the kernel is rank (rank + i) % world
+    for (int i = 0; i < c.world; ++i) {
+        const int src = (c.rank + i) % c.world;
+        unsigned char* k_dst = h->k_slot(h->buf, set, src);
+        unsigned char* v_dst = h->v_slot(h->buf, set, src);
+        if (i > 0) {
+            cudaError_t e = cudaMemcpyAsync(k_dst, h->k_slot(h->peer[src], set, src), h->shard_bytes,
+                                            cudaMemcpyDeviceToDevice, ps);
+            if (e == cudaSuccess)
+                e = cudaMemcpyAsync(v_dst, h->v_slot(h->peer[src], set, src), h->shard_bytes,
+                                    cudaMemcpyDeviceToDevice, ps);
+            if (e != cudaSuccess) return fail_cuda(h, "peer copy", e);
+            if (h->write32(reinterpret_cast<CUstream>(ps), reinterpret_cast<CUdeviceptr>(h->flag(set, src)),
+                           h->epoch, 0) != CUDA_SUCCESS)
+                return fail(h, F2K_ERR_CUDA, "cuStreamWriteValue32 failed");
+            p.kv_ready[i] = overlap ? h->flag(set, src) : nullptr;
+        }
+        if (!encode(h, &p.tm_k[i], k_dst, c.seq_local) || !encode(h, &p.tm_v[i], v_dst, c.seq_local))
+            return fail(h, F2K_ERR_CUDA, "tensor map (K/V) failed");
+        p.kv_len[i] = c.seq_local;
+        p.kv_tile_start[i] = i * tiles_per_seg;
+    }
+    p.kv_tile_start[c.world] = c.world * tiles_per_seg;
+    p.n_kvseg = c.world;
+    p.n_kv_tiles = c.world * tiles_per_seg;
+    p.kv_ready_value = h->epoch;
+    p.n_heads = c.n_heads;
+    p.batch = c.batch;
+    p.scale_log2 = h->scale * 1.4426950408889634f;
+    p.status = h->d_status;
+
+    if (c.world > 1 && !overlap) {
+        cudaError_t e = cudaEventRecord(h->pulled, ps);
+        if (e == cudaSuccess) e = cudaStreamWaitEvent(cs, h->pulled, 0);
+        if (e != cudaSuccess) return fail_cuda(h, "event", e);
+    }
+    const cudaError_t e = attn_fwd_launch(p, cs);
+    if (e != cudaSuccess) return fail_cuda(h, "attention launch", e);
+    return F2K_OK;
+}
+
+int f2k_seqpar_device_status(f2k_seqpar* h, int* status_out) {
+    if (!h || !h->valid) return F2K_ERR_INVALID;
+    int st = 0;
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return fail_cuda(h, "cudaDeviceSynchronize", e);
+    e = cudaMemcpy(&st, h->d_status, sizeof st, cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return fail_cuda(h, "status read", e);
+    if (st != 0) cudaMemset(h->d_status, 0, sizeof st);
+    if (status_out) *status_out = st;
+    if (st != 0) return fail(h, F2K_ERR_DEVICE, "a bounded wait inside the attention kernel expired");
+    return F2K_OK;
+}
+
+// ---- CUDA IPC helpers (one process per GPU: the allocation of a rank, mapped into its peers) ----
+int f2k_ipc_export(const void* base, void* handle64) {
+    if (!base || !handle64) return F2K_ERR_INVALID;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+    cudaIpcMemHandle_t hd;
+    if (cudaIpcGetMemHandle(&hd, const_cast<void*>(base)) != cudaSuccess) return F2K_ERR_CUDA;
+    std::memcpy(handle64, &hd, 64);
+    return F2K_OK;
+}
+int f2k_ipc_open(const void* handle64, void** base) {
+    if (!handle64 || !base) return F2K_ERR_INVALID;
+    cudaIpcMemHandle_t hd;
+    std::memcpy(&hd, handle64, 64);
+    return cudaIpcOpenMemHandle(base, hd, cudaIpcMemLazyEnablePeerAccess) == cudaSuccess ? F2K_OK : F2K_ERR_CUDA;
+}
+int f2k_ipc_close(void* base) {
+    if (!base) return F2K_ERR_INVALID;
+    return cudaIpcCloseMemHandle(base) == cudaSuccess ? F2K_OK : F2K_ERR_CUDA;
+}
+
+// ---- the prologue kernel on its own: y = RoPE(RMSNorm(x) * gamma), position = token index ----
+int f2k_qk_norm_rope_bf16(const void* x, void* y, const void* gamma, const float* cos_table,
+                          const float* sin_table, int batch, int seq, int n_heads, float eps, void* stream) {
+    if (!x || !y || !gamma || !cos_table || !sin_table) return F2K_ERR_INVALID;
+    if (batch <= 0 || seq <= 0 || n_heads <= 0) return F2K_ERR_INVALID;
+    QkPrologueParams pp;
+    std::memset(&pp, 0, sizeof pp);
+    pp.job[0].x = x; pp.job[0].y = y; pp.job[0].gamma = gamma;
+    pp.job[0].cos_tab = cos_table; pp.job[0].sin_tab = sin_table; pp.job[0].seq = seq;
+    pp.job[0].rows = (long long)batch * seq * n_heads;
+    pp.row_start[0] = 0; pp.row_start[1] = pp.job[0].rows;
+    pp.n_jobs = 1; pp.n_heads = n_heads; pp.eps = eps;
+    return qk_prologue_launch(pp, static_cast<cudaStream_t>(stream)) == cudaSuccess ? F2K_OK : F2K_ERR_CUDA;
+}
+
+}  // extern "C"

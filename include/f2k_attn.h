@@ -168,6 +168,57 @@ int f2k_build_rope_4axis_tables(const int* axes_dim, int n_axes,
                                 const int* positions, int seq, float theta,
                                 float* cos_out, float* sin_out);
 
+/* ---- sequence-parallel attention over the GPUs of one box --------------------------------
+ * None of this has a counterpart in the reference, which runs on a single GPU. Tokens are
+ * sharded by rank (one process per GPU); every rank attends its seq_local queries to the keys
+ * and values of all ranks. Remote K/V shards are pulled into local memory by the copy engines
+ * over NVLink while the attention kernel already works on the shards that have arrived.
+ * Call order per step: write this rank's normalised K and its V to the pointers given by
+ * f2k_seqpar_local_kv -> cross-rank barrier (the host's job, e.g. an all-reduce on the compute
+ * stream) -> f2k_seqpar_forward. */
+typedef struct f2k_seqpar f2k_seqpar; /* opaque */
+
+typedef struct f2k_seqpar_config {
+    int   batch;
+    int   seq_local; /* tokens held by every rank */
+    int   n_heads;
+    int   head_dim;  /* 128 */
+    int   world;     /* 1..8 ranks */
+    int   rank;
+    float scale;     /* <= 0 selects 1/sqrt(head_dim) */
+} f2k_seqpar_config;
+
+/* Allocates this rank's shard buffer (4 * world * B * seq_local * n_heads * 128 * 2 bytes). */
+int         f2k_seqpar_create(const f2k_seqpar_config* cfg, f2k_seqpar** out);
+void        f2k_seqpar_destroy(f2k_seqpar* h);
+const char* f2k_seqpar_last_error(const f2k_seqpar* h);
+/* Base and size of this rank's shard buffer (to be exported to the peers). */
+int f2k_seqpar_buffer(f2k_seqpar* h, void** base, size_t* bytes);
+/* peer_bases[r] = rank r's shard buffer as addressable from this process (entry `rank` is
+ * ignored): an f2k_ipc_open mapping, or the pointer itself when ranks share a process. */
+int f2k_seqpar_attach(f2k_seqpar* h, void* const* peer_bases);
+/* Where this rank's K (normalised, rotated) and V for the next forward call have to be written. */
+int f2k_seqpar_local_kv(f2k_seqpar* h, void** k, void** v);
+/* q_local, o_local: [batch, seq_local, n_heads, 128] bf16. overlap != 0: the kernel starts at
+ * once and waits per shard for its arrival; overlap == 0: it starts after all pulls. */
+int f2k_seqpar_forward(f2k_seqpar* h, const void* q_local, void* o_local, int overlap,
+                       void* compute_stream, void* copy_stream);
+int f2k_seqpar_device_status(f2k_seqpar* h, int* status_out);
+
+/* CUDA IPC for the shard buffers: 64-byte handles to pass between the rank processes. */
+int f2k_ipc_export(const void* base, void* handle64);
+int f2k_ipc_open(const void* handle64, void** base);
+int f2k_ipc_close(void* base);
+
+/* The fused prologue kernel on its own: y = RoPE(RMSNorm(x) * gamma) per 128-element head row of
+ * x [batch, seq, n_heads, 128], position of a token = its index in seq (pass the rank's slice of
+ * the tables). Same arithmetic as the prologue inside f2k_attn_forward_fused; stands in for
+ * rmsnorm_bf16 + rope_4axis_inplace_bf16 + fill_pos_ids_expanded of the reference callers
+ * (src/backend/cuda/double_stream_block.cu:290-372). y may alias x. */
+int f2k_qk_norm_rope_bf16(const void* x, void* y, const void* gamma, const float* cos_table,
+                          const float* sin_table, int batch, int seq, int n_heads, float eps,
+                          void* stream);
+
 /* Library identification string (static storage). */
 const char* f2k_attn_version(void);
 
