@@ -61,7 +61,7 @@ constexpr float kLazyThreshold = 8.0f;  // log2 units
 #define F2K_OPT_SETMAXNREG 1   // softmax warpgroups take registers from the load/MMA warpgroup
 #endif
 #ifndef F2K_OPT_P_PARTS
-#define F2K_OPT_P_PARTS 2      // P is handed to the MMA warp in this many parts (1, 2 or 4)
+#define F2K_OPT_P_PARTS 4      // P is handed to the MMA warp in this many parts (1, 2 or 4)
 #endif
 #ifndef F2K_OPT_POLY_OF8
 #define F2K_OPT_POLY_OF8 0     // of every 8 key pairs, how many take 2^x on the FMA pipe (0..8)
@@ -409,7 +409,10 @@ attn_fwd_sm100_kernel(const __grid_constant__ AttnParams p) {
             PH_MARK(ph_base + 0);   // waiting for S
             tc_fence_after_sync();
 
+            // The row is fetched in two halves: the maxima of the first 64 scores are folded while
+            // the second 64 are still on their way from tensor memory.
             uint32_t s[128];
+            float mx[8];
             {
                 uint32_t(&s0)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[0]);
                 uint32_t(&s1)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[32]);
@@ -417,18 +420,25 @@ attn_fwd_sm100_kernel(const __grid_constant__ AttnParams p) {
                 uint32_t(&s3)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[96]);
                 tmem_ld_x32(tS + 0, s0);
                 tmem_ld_x32(tS + 32, s1);
+                tmem_wait_ld();
                 tmem_ld_x32(tS + 64, s2);
                 tmem_ld_x32(tS + 96, s3);
+                if (valid < 64) {  // last tile of a segment: keys past its end do not exist
+#pragma unroll
+                    for (int i = 0; i < 64; ++i)
+                        if (i >= valid) s[i] = __float_as_uint(-INFINITY);
+                }
+                row_max64<true>(&s[0], mx);
                 tmem_wait_ld();
             }
             PH_MARK(ph_base + 1);   // S -> registers
-            if (valid < kTileN) {  // last tile of a segment: keys past its end do not exist
+            if (valid < kTileN) {
 #pragma unroll
-                for (int i = 0; i < 128; ++i)
+                for (int i = 64; i < 128; ++i)
                     if (i >= valid) s[i] = __float_as_uint(-INFINITY);
             }
-
-            const float m_tile = row_max128(s);
+            row_max64<false>(&s[64], mx);
+            const float m_tile = row_max_finish(mx);
 
             const bool need = (m_tile - m_ref) * c > kLazyThreshold;
             if (__any_sync(0xffffffffu, need)) {
@@ -455,20 +465,31 @@ attn_fwd_sm100_kernel(const __grid_constant__ AttnParams p) {
             // per column); the row sum keeps the unrounded values.
             const float neg_mc = -m_ref * c;
             float sum[4] = {0.f, 0.f, 0.f, 0.f};
+            // A part of P is announced half a chunk after its last store was issued: by then the
+            // store has drained, so the wait costs nothing and the special-function unit never
+            // idles behind it. Only the last part has to wait for real.
+            int pending = -1;
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
                 uint32_t pk[16];
-                exp_chunk32<F2K_OPT_POLY_OF8>(&s[q * 32], pk, c, neg_mc, sum);
-                tmem_st_x16(tS + q * 16, pk);
-                if ((q + 1) % (4 / kPParts) == 0) {   // this part of the keys is ready for the MMA warp
-                    PH_MARK(ph_base + 3);   // exponentials
+                exp_chunk16<F2K_OPT_POLY_OF8>(&s[q * 32], pk, c, neg_mc, sum);
+                if (pending >= 0) {
                     tmem_wait_st();
                     tc_fence_before_sync();
-                    mbar_arrive(smem_u32(&ctl->p_full[t][(q + 1) / (4 / kPParts) - 1]));
-                    if ((warp & 3) == 0) PH_EVENT(30 + t * 4 + (q + 1) / (4 / kPParts) - 1, j);   // softmax t: part handed over
-                    PH_MARK(ph_base + 4);   // store drain + hand-over
+                    mbar_arrive(smem_u32(&ctl->p_full[t][0]) + pending * 8);
+                    if ((warp & 3) == 0) PH_EVENT(30 + t * 4 + pending, j);   // softmax t: part handed over
+                    pending = -1;
                 }
+                exp_chunk16<F2K_OPT_POLY_OF8>(&s[q * 32 + 16], pk + 8, c, neg_mc, sum);
+                tmem_st_x16(tS + q * 16, pk);
+                if ((q + 1) % (4 / kPParts) == 0) pending = (q + 1) / (4 / kPParts) - 1;
             }
+            PH_MARK(ph_base + 3);   // exponentials
+            tmem_wait_st();
+            tc_fence_before_sync();
+            mbar_arrive(smem_u32(&ctl->p_full[t][kPParts - 1]));
+            if ((warp & 3) == 0) PH_EVENT(30 + t * 4 + kPParts - 1, j);
+            PH_MARK(ph_base + 4);   // last store drain + hand-over
             l_sum += (sum[0] + sum[1]) + (sum[2] + sum[3]);
         }
 

@@ -1,5 +1,5 @@
 // Inline-PTX wrappers for the sm_100a features the joint-attention kernels use:
-// mbarrier, TMA tiled loads (cp.async.bulk.tensor, never with cluster multicast),
+// mbarrier, TMA tiled loads (plain cp.async.bulk.tensor into the issuing CTA only),
 // tensor memory (TMEM) allocation and access, and tcgen05 MMA issue/commit.
 //
 // Every wait on an mbarrier is bounded: on expiry the caller gets `false`, records
@@ -110,7 +110,7 @@ __device__ __forceinline__ bool global_flag_wait(const unsigned int* flag, unsig
 }
 
 // ----------------------------------------------------------------------------
-// TMA (tiled, 4-D, global -> shared, completion on an mbarrier). No multicast.
+// TMA (tiled, 4-D, global -> shared, completion on an mbarrier). One destination CTA.
 // ----------------------------------------------------------------------------
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");

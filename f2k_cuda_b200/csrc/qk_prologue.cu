@@ -79,13 +79,17 @@ __device__ __forceinline__ float warp_sum(float v) {
 // elements [8i, 8i+8) = rotation pairs 4i .. 4i+3, so both the reduction and the
 // rotation stay inside the half-warp and inside a lane respectively.
 // ---------------------------------------------------------------------------------
-__global__ void __launch_bounds__(kBlock)
+// A half-warp takes kGroup consecutive head rows of ONE token per iteration (kGroup divides the
+// head count): their loads are issued back to back (kGroup x 16 bytes in flight per lane), and the
+// token's table row and the gains are fetched once for the group.
+template <int kGroup>
+__global__ void __launch_bounds__(kBlock, 4)
 qk_prologue_kernel(const __grid_constant__ QkPrologueParams p) {
     const int hl = threadIdx.x & 15;  // lane inside the half-warp
-    const long long total = p.row_start[p.n_jobs];
+    const long long total = p.row_start[p.n_jobs] / kGroup;          // in groups
     const long long n_hw  = (long long)gridDim.x * (kBlock / 16);
-    for (long long row = (long long)blockIdx.x * (kBlock / 16) + (threadIdx.x >> 4);
-         row < total; row += n_hw) {
+    for (long long grp = (long long)blockIdx.x * (kBlock / 16) + (threadIdx.x >> 4); grp < total; grp += n_hw) {
+        const long long row = grp * kGroup;
         int j = 0;
 #pragma unroll
         for (int i = 1; i < kMaxPrologueJobs; ++i)
@@ -93,33 +97,37 @@ qk_prologue_kernel(const __grid_constant__ QkPrologueParams p) {
         const QkPrologueJob& job = p.job[j];
         const long long lr = row - p.row_start[j];
         const int tok = (int)((lr / p.n_heads) % job.seq);
-
-        // plain load: y may alias x, so x is not read-only for the kernel's lifetime
-        const uint4 raw = reinterpret_cast<const uint4*>(
-            static_cast<const __nv_bfloat16*>(job.x) + lr * kHeadDim)[hl];
-        const uint4 graw = __ldg(reinterpret_cast<const uint4*>(job.gamma) + hl);
+        // plain loads of x: y may alias x, so x is not read-only for the kernel's lifetime
+        const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(job.x) + lr * kHeadDim);
+        uint4 raw[kGroup];
+#pragma unroll
+        for (int u = 0; u < kGroup; ++u) raw[u] = src[u * 16 + hl];
+        const uint4  graw = __ldg(reinterpret_cast<const uint4*>(job.gamma) + hl);
         const float4 c4 = __ldg(reinterpret_cast<const float4*>(job.cos_tab + (long long)tok * 64) + hl);
         const float4 s4 = __ldg(reinterpret_cast<const float4*>(job.sin_tab + (long long)tok * 64) + hl);
-
-        float v[8], g[8];
-        unpack8(raw, v);
+        float g[8];
         unpack8(graw, g);
-        float ss = 0.f;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) ss = fmaf(v[i], v[i], ss);
-        ss = half_warp_sum(ss);
-        const float rrms = rsqrtf(ss * (1.0f / kHeadDim) + p.eps);
-
         const float cs[4] = {c4.x, c4.y, c4.z, c4.w};
         const float sn[4] = {s4.x, s4.y, s4.z, s4.w};
-        float y[8];
+        uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(job.y) + lr * kHeadDim);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const float a = v[2 * k] * rrms * g[2 * k];
-            const float b = v[2 * k + 1] * rrms * g[2 * k + 1];
-            rotate_pair(y[2 * k], y[2 * k + 1], a, b, cs[k], sn[k]);
+        for (int u = 0; u < kGroup; ++u) {
+            float v[8];
+            unpack8(raw[u], v);
+            float ss = 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ss = fmaf(v[i], v[i], ss);
+            ss = half_warp_sum(ss);
+            const float rrms = rsqrtf(ss * (1.0f / kHeadDim) + p.eps);
+            float y[8];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float a = v[2 * k] * rrms * g[2 * k];
+                const float b = v[2 * k + 1] * rrms * g[2 * k + 1];
+                rotate_pair(y[2 * k], y[2 * k + 1], a, b, cs[k], sn[k]);
+            }
+            dst[u * 16 + hl] = pack8(y);
         }
-        reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(job.y) + lr * kHeadDim)[hl] = pack8(y);
     }
 }
 
@@ -246,7 +254,7 @@ int grid_for(long long units, int units_per_block) {
             sms = 148;
     }
     const long long need = (units + units_per_block - 1) / units_per_block;
-    const long long cap  = (long long)sms * 8;  // 8 x 256 threads = a full SM
+    const long long cap  = (long long)sms * 8;  // 8 x 256 threads = a full SM of resident threads
     return (int)(need < cap ? (need > 0 ? need : 1) : cap);
 }
 
@@ -255,7 +263,10 @@ int grid_for(long long units, int units_per_block) {
 cudaError_t qk_prologue_launch(const QkPrologueParams& p, cudaStream_t stream) {
     const long long total = p.row_start[p.n_jobs];
     if (total <= 0) return cudaSuccess;
-    qk_prologue_kernel<<<grid_for(total, kBlock / 16), kBlock, 0, stream>>>(p);
+    if (p.n_heads % 4 == 0)
+        qk_prologue_kernel<4><<<grid_for(total / 4, kBlock / 16), kBlock, 0, stream>>>(p);
+    else
+        qk_prologue_kernel<1><<<grid_for(total, kBlock / 16), kBlock, 0, stream>>>(p);
     return cudaPeekAtLastError();
 }
 

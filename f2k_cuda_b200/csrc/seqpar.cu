@@ -16,7 +16,7 @@
 // compute stream with one key/value segment per rank: its own first, then the others in the
 // order they arrive; its TMA producer waits (bounded) on a segment's arrival word before the
 // first tile of that segment. So the transfer of shard i+1 overlaps the MMAs on shard i, remote
-// data is only ever read from local memory by ordinary non-multicast TMA, and nothing waits on
+// data is only ever read from local memory by ordinary single-CTA TMA loads, and nothing waits on
 // another kernel. With overlap off the compute stream simply waits for all pulls.
 //
 // Two sets: a rank may start writing the next call's K/V while slower peers still pull the

@@ -1,7 +1,7 @@
 // Per-row softmax arithmetic of the attention kernel: a thread owns one query row of a
 // 128-key tile in registers (fp32 scores as loaded from tensor memory).
 //
-//   row_max128      maximum of the 128 scores
+//   row_max64/128   maximum of the scores (8 independent chains)
 //   exp_chunk32     P = 2^(c*s + neg_mc) for 32 scores -> 16 packed bf16 pairs, and the sum of
 //                   the unrounded values (four partial sums)
 //
@@ -15,18 +15,28 @@
 
 namespace f2k {
 
-__device__ __forceinline__ float row_max128(const uint32_t (&s)[128]) {
+// Running maxima of 64 scores folded into 8 independent chains (3-input max, two new scores per
+// step and chain); `first` starts the chains.
+template <bool kFirst>
+__device__ __forceinline__ void row_max64(const uint32_t* s, float (&m)[8]) {
     using namespace f2k::ptx;
-    float m[8];
 #pragma unroll
-    for (int k = 0; k < 8; ++k)
-        m[k] = fmaxf(__uint_as_float(s[2 * k]), __uint_as_float(s[2 * k + 1]));
+    for (int i = 0; i < 64; i += 16)
 #pragma unroll
-    for (int i = 16; i < 128; i += 16)
-#pragma unroll
-        for (int k = 0; k < 8; ++k)
-            m[k] = fmax3(m[k], __uint_as_float(s[i + 2 * k]), __uint_as_float(s[i + 2 * k + 1]));
+        for (int k = 0; k < 8; ++k) {
+            const float a = __uint_as_float(s[i + 2 * k]), b = __uint_as_float(s[i + 2 * k + 1]);
+            m[k] = (kFirst && i == 0) ? fmaxf(a, b) : fmax3(m[k], a, b);
+        }
+}
+__device__ __forceinline__ float row_max_finish(const float (&m)[8]) {
+    using namespace f2k::ptx;
     return fmaxf(fmax3(m[0], m[1], m[2]), fmax3(fmax3(m[3], m[4], m[5]), m[6], m[7]));
+}
+__device__ __forceinline__ float row_max128(const uint32_t (&s)[128]) {
+    float m[8];
+    row_max64<true>(&s[0], m);
+    row_max64<false>(&s[64], m);
+    return row_max_finish(m);
 }
 
 // 2^x for a pair on the FMA pipe. x = n + f by the 1.5*2^23 rounding trick, cubic fit of 2^f on
@@ -48,12 +58,14 @@ __device__ __forceinline__ void exp2_fma_pair(float& r0, float& r1, float x0, fl
     r1 = __uint_as_float((__float_as_uint(t1) << 23) + __float_as_uint(p1));
 }
 
+// 16 scores -> 8 packed bf16 pairs. `pair0` is the index of the first pair inside its group of 8
+// pairs (0 or 8 key pairs into a 32-key chunk), which decides who takes the polynomial.
 template <int kPolyOf8>
-__device__ __forceinline__ void exp_chunk32(const uint32_t* s, uint32_t (&pk)[16], float c,
-                                            float neg_mc, float (&sum)[4]) {
+__device__ __forceinline__ void exp_chunk16(const uint32_t* s, uint32_t* pk, float c, float neg_mc,
+                                            float (&sum)[4]) {
     using namespace f2k::ptx;
 #pragma unroll
-    for (int i = 0; i < 32; i += 4) {
+    for (int i = 0; i < 16; i += 4) {
         float x0, x1, x2, x3;
         fma2(x0, x1, __uint_as_float(s[i + 0]), __uint_as_float(s[i + 1]), c, c, neg_mc, neg_mc);
         fma2(x2, x3, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]), c, c, neg_mc, neg_mc);
@@ -72,6 +84,13 @@ __device__ __forceinline__ void exp_chunk32(const uint32_t* s, uint32_t (&pk)[16
         pk[i / 2 + 0] = pack_bf16x2(p0, p1);
         pk[i / 2 + 1] = pack_bf16x2(p2, p3);
     }
+}
+
+template <int kPolyOf8>
+__device__ __forceinline__ void exp_chunk32(const uint32_t* s, uint32_t (&pk)[16], float c,
+                                            float neg_mc, float (&sum)[4]) {
+    exp_chunk16<kPolyOf8>(s, pk, c, neg_mc, sum);
+    exp_chunk16<kPolyOf8>(s + 16, pk + 8, c, neg_mc, sum);
 }
 
 }  // namespace f2k
