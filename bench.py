@@ -50,6 +50,10 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="s4608", choices=["s4608", "s8704_seqpar", "s16896_seqpar"],
+                    help="s4608: the headline shape (heads sharded over the GPUs). *_seqpar: the long shapes with the "
+                         "sequence sharded over the GPUs (strong scaling, K/V pulled over NVLink under the kernel)")
+    ap.add_argument("--no-overlap", action="store_true", help="seqpar: start the kernel only after all K/V pulls")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the timed CPU leg")
     ap.add_argument("--skip-e2e", action="store_true",
                     help="skip the host-buffer leg (for short profiler captures; the line then has e2e null)")
@@ -291,6 +295,104 @@ def run_ours(args, rank, world):
     return line
 
 
+def run_seqpar(args, rank, world):
+    """Sequence-parallel attention on the 8704- / 16896-token shapes, batch 1, 32 heads: every rank
+    owns S/world tokens. Step = QK-norm + RoPE of the local Q and K, the cross-rank "K/V written"
+    barrier (one 4-byte all-reduce), the pulls of the other ranks' K/V shards by the copy engines and
+    the attention kernel that consumes them as they arrive. V is already in the shard buffer (where a
+    V projection would write it). Strong scaling: the total work is fixed."""
+    import f2k_cuda_b200 as f2k
+    from f2k_cuda_b200.inputs import WORKLOADS, make_problem, token_positions
+    from f2k_cuda_b200.seqpar import SequenceParallelAttention, qk_norm_rope, shard_bounds
+    w = WORKLOADS["s16896" if args.workload.startswith("s16896") else "s8704_edit"]
+    S, H, D = w.seq, w.n_heads, w.head_dim
+    if S % world != 0:
+        raise SystemExit(f"{S} tokens do not split evenly over {world} ranks")
+    per = S // world
+    b, e = shard_bounds(S, world, rank)
+    stream = torch.cuda.current_stream()
+    # this rank's tokens only: positions decide which stream (text or image) a token belongs to
+    pt, pi = token_positions(w)
+    cos_t, sin_t = f2k.build_rope_4axis_tables((32,) * 4, pt, 2000.0)
+    cos_i, sin_i = f2k.build_rope_4axis_tables((32,) * 4, pi, 2000.0)
+    cos = np.concatenate([cos_t, cos_i])[b:e]
+    sin = np.concatenate([sin_t, sin_i])[b:e]
+    n_txt = max(0, min(e, w.seq_txt) - b)           # text tokens in this shard (they come first)
+    gen = torch.Generator(device="cuda").manual_seed(1234 + rank)
+    mk = lambda: torch.randn(1, per, H, D, device="cuda", generator=gen).to(torch.bfloat16)  # noqa: E731
+    q_raw, k_raw, v = mk(), mk(), mk()
+    p = make_problem(WORKLOADS["s1152"], heads=1)    # only for the four gain vectors
+    g = [dev_bf16(x) for x in p.gammas]
+    dcos, dsin = torch.from_numpy(cos).cuda(), torch.from_numpy(sin).cuda()
+    sp = SequenceParallelAttention(1, per, H, D, world, rank)
+    if not sp.ok():
+        raise RuntimeError(sp.last_error())
+    ok = sp.attach_distributed() if world > 1 else sp.attach_in_process([sp])
+    if not ok:
+        raise RuntimeError("attaching the peers' shard buffers failed: " + sp.last_error())
+    qn, o = torch.empty_like(q_raw), torch.empty_like(q_raw)
+    token = torch.ones(1, device="cuda")
+    for _ in range(2):                                # V into both buffer sets
+        ks, vs = sp.local_kv()
+        vs.copy_(v)
+        ks.zero_()
+        if world > 1:
+            torch.distributed.all_reduce(token, op=torch.distributed.ReduceOp.MAX)
+        sp.forward(q_raw, o, overlap=False)
+    torch.cuda.synchronize()
+
+    def norm_rope(x, y, gq_txt, gq_img):
+        okk = True
+        if n_txt > 0:
+            okk &= qk_norm_rope(x[:, :n_txt], y[:, :n_txt], gq_txt, dcos[:n_txt], dsin[:n_txt], 1e-6)
+        if n_txt < per:
+            okk &= qk_norm_rope(x[:, n_txt:], y[:, n_txt:], gq_img, dcos[n_txt:], dsin[n_txt:], 1e-6)
+        return okk
+
+    def step():
+        ks, _ = sp.local_kv()
+        okk = norm_rope(q_raw, qn, g[0], g[2]) and norm_rope(k_raw, ks, g[1], g[3])
+        if world > 1:
+            torch.distributed.all_reduce(token, op=torch.distributed.ReduceOp.MAX)        # every rank's K (and V) is in its slot
+        okk = okk and sp.forward(qn, o, overlap=not args.no_overlap)
+        if not okk:
+            raise RuntimeError(sp.last_error())
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    if sp.device_status() != 0:
+        raise RuntimeError("attention kernel reported a device-side error during warm-up")
+    sampler = ClockSampler(torch.cuda.current_device()) if rank == 0 else None
+    if world > 1:
+        torch.distributed.barrier()
+    ms = time_region(step, args.steps, stream)
+    if world > 1:
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        ms = float(t.item())
+    clocks = sampler.stop() if sampler else None
+    if sp.device_status() != 0:
+        raise RuntimeError("attention kernel reported a device-side error")
+    if rank != 0:
+        return None
+    flops = 4.0 * H * float(S) ** 2 * D                # whole job
+    peak, peak_src = measured_peak()
+    return {
+        "metric": METRIC, "value": flops / (ms * 1e-3) / 1e12, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"{w.name}: {S} tokens, batch 1, 32 heads, hd128, sequence sharded {per} tokens per GPU",
+                   "step": "QK-RMSNorm + RoPE of the local Q, K; barrier; copy-engine pulls of the remote K/V shards "
+                           + ("after which" if args.no_overlap else "under") + " the attention kernel",
+                   "flops_per_step_total": flops, "parallelism": f"seq{world}",
+                   "nvlink_bytes_per_gpu_per_step": 2 * (world - 1) * per * H * D * 2,
+                   "l2": "K/V of all ranks (%.0f MB) exceed the 126 MB L2" % (2 * S * H * D * 2 / 1e6)},
+        "per_gpu_tflops": flops / world / (ms * 1e-3) / 1e12,
+        "pct_of_peak": 100.0 * flops / world / (ms * 1e-3) / 1e12 / peak, "peak_source": peak_src,
+        "e2e": None, "gpu_launches": (4 if 0 < n_txt < per else 2) * args.steps + args.steps, "clocks": clocks,
+    }
+
+
 def run_reference(args, rank, world):
     """The reference's own implementation of the path: its CUDA kernels (rmsnorm_bf16 x4,
     rope_4axis_inplace_bf16 x4, JointAttention::forward with its concat/split copies), rebuilt
@@ -415,7 +517,12 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local))
     try:
-        line = run_ours(args, rank, world) if args.impl == "ours" else run_reference(args, rank, world)
+        if args.impl == "reference":
+            line = run_reference(args, rank, world)
+        elif args.workload == "s4608":
+            line = run_ours(args, rank, world)
+        else:
+            line = run_seqpar(args, rank, world)
         if line is not None:
             print(json.dumps(line), flush=True)
     finally:

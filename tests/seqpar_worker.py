@@ -31,7 +31,7 @@ def main():
     for step, overlap in enumerate((True, False, True)):
         ks, vs = sp.local_kv()
         ks.copy_(dev_bf16(k[:, b:e])); vs.copy_(dev_bf16(v[:, b:e]))
-        dist.all_reduce(token)                  # every rank's K/V is written (stream-ordered)
+        dist.all_reduce(token, op=dist.ReduceOp.MAX)                  # every rank's K/V is written (stream-ordered)
         do = torch.full_like(dq, float("nan"))
         assert sp.forward(dq, do, overlap=overlap), sp.last_error()
         torch.cuda.synchronize()
