@@ -297,9 +297,9 @@ def run_ours(args, rank, world):
 
 def run_seqpar(args, rank, world):
     """Sequence-parallel attention on the 8704- / 16896-token shapes, batch 1, 32 heads: every rank
-    owns S/world tokens. Step = QK-norm + RoPE of the local Q and K, the cross-rank "K/V written"
-    barrier (one 4-byte all-reduce), the pulls of the other ranks' K/V shards by the copy engines and
-    the attention kernel that consumes them as they arrive. V is already in the shard buffer (where a
+    owns S/world tokens. Step = QK-norm + RoPE of the local Q and K, the pulls of the other ranks'
+    K/V shards by the copy engines (readiness is exchanged as words in the shard buffers, no
+    collective) and the attention kernel that consumes them as they arrive. V is already in the shard buffer (where a
     V projection would write it). Strong scaling: the total work is fixed."""
     import f2k_cuda_b200 as f2k
     from f2k_cuda_b200.inputs import WORKLOADS, make_problem, token_positions
@@ -331,13 +331,10 @@ def run_seqpar(args, rank, world):
     if not ok:
         raise RuntimeError("attaching the peers' shard buffers failed: " + sp.last_error())
     qn, o = torch.empty_like(q_raw), torch.empty_like(q_raw)
-    token = torch.ones(1, device="cuda")
     for _ in range(2):                                # V into both buffer sets
         ks, vs = sp.local_kv()
         vs.copy_(v)
         ks.zero_()
-        if world > 1:
-            torch.distributed.all_reduce(token, op=torch.distributed.ReduceOp.MAX)
         sp.forward(q_raw, o, overlap=False)
     torch.cuda.synchronize()
 
@@ -352,8 +349,6 @@ def run_seqpar(args, rank, world):
     def step():
         ks, _ = sp.local_kv()
         okk = norm_rope(q_raw, qn, g[0], g[2]) and norm_rope(k_raw, ks, g[1], g[3])
-        if world > 1:
-            torch.distributed.all_reduce(token, op=torch.distributed.ReduceOp.MAX)        # every rank's K (and V) is in its slot
         okk = okk and sp.forward(qn, o, overlap=not args.no_overlap)
         if not okk:
             raise RuntimeError(sp.last_error())
@@ -382,7 +377,7 @@ def run_seqpar(args, rank, world):
         "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"{w.name}: {S} tokens, batch 1, 32 heads, hd128, sequence sharded {per} tokens per GPU",
-                   "step": "QK-RMSNorm + RoPE of the local Q, K; barrier; copy-engine pulls of the remote K/V shards "
+                   "step": "QK-RMSNorm + RoPE of the local Q, K; copy-engine pulls of the remote K/V shards "
                            + ("after which" if args.no_overlap else "under") + " the attention kernel",
                    "flops_per_step_total": flops, "parallelism": f"seq{world}",
                    "nvlink_bytes_per_gpu_per_step": 2 * (world - 1) * per * H * D * 2,

@@ -246,7 +246,8 @@ attn_fwd_sm100_kernel(const __grid_constant__ AttnParams p) {
                     if (row0 == 0 && p.kv_ready[seg] != nullptr) {
                         // first tile of a segment that is being copied in: wait for its arrival word,
                         // then order the copy engine's writes before this thread's TMA reads
-                        ok = global_flag_wait(p.kv_ready[seg], p.kv_ready_value, abort_flag);
+                        ok = global_flag_wait(p.kv_ready[seg] + head / max(1, p.kv_ready_heads_per_group),
+                                              p.kv_ready_value, abort_flag);
                         if (!ok) break;
                         asm volatile("fence.proxy.async.global;" ::: "memory");
                     }
@@ -544,18 +545,30 @@ attn_fwd_sm100_kernel(const __grid_constant__ AttnParams p) {
 
 size_t attn_fwd_smem_bytes() { return kSmemUsed + 1024; }
 
-cudaError_t attn_fwd_launch(const AttnParams& p, cudaStream_t stream) {
+// Loads the kernel on the current device and raises its shared-memory limit. Called when a
+// handle is created, so that the first launch does not have to load code: loading may
+// synchronise the device, which must not happen while a stream is parked on a wait that only a
+// later call (or another process) can satisfy.
+cudaError_t attn_fwd_prepare() {
     static bool configured[64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
+    if (dev < 64 && configured[dev]) return cudaSuccess;
+    e = cudaFuncSetAttribute(attn_fwd_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)attn_fwd_smem_bytes());
+    if (e != cudaSuccess) return e;
+    cudaFuncAttributes attr;
+    e = cudaFuncGetAttributes(&attr, attn_fwd_sm100_kernel);
+    if (e != cudaSuccess) return e;
+    if (dev < 64) configured[dev] = true;
+    return cudaSuccess;
+}
+
+cudaError_t attn_fwd_launch(const AttnParams& p, cudaStream_t stream) {
+    cudaError_t e = attn_fwd_prepare();
+    if (e != cudaSuccess) return e;
     const size_t smem = attn_fwd_smem_bytes();
-    if (dev < 64 && !configured[dev]) {
-        e = cudaFuncSetAttribute(attn_fwd_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)smem);
-        if (e != cudaSuccess) return e;
-        configured[dev] = true;
-    }
     dim3 grid((p.n_q_tiles + 1) / 2, p.n_heads, p.batch);
     attn_fwd_sm100_kernel<<<grid, kThreads, smem, stream>>>(p);
     return cudaPeekAtLastError();

@@ -11,6 +11,7 @@ namespace f2k {
 
 // tcgen05 flash-attention forward (attn_fwd_sm100.cu).
 size_t      attn_fwd_smem_bytes();
+cudaError_t attn_fwd_prepare();   // load + configure the kernel on the current device (idempotent)
 cudaError_t attn_fwd_launch(const AttnParams& p, cudaStream_t stream);
 
 // Fused per-head RMSNorm + 4-axis RoPE for the Q and K of up to two streams in one
@@ -33,6 +34,7 @@ struct QkPrologueParams {
     float         eps;
 };
 cudaError_t qk_prologue_launch(const QkPrologueParams& p, cudaStream_t stream);
+cudaError_t qk_prologue_prepare();   // load the prologue kernels on the current device
 
 // Stand-alone kernels with the reference's call shapes (qk_prologue.cu).
 cudaError_t rmsnorm_rows_launch(const void* x, const void* gamma, void* y, int rows, int dim,

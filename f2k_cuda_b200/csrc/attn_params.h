@@ -54,12 +54,14 @@ struct AttnParams {
     int* status;                      // device word, AttnStatus bits OR-ed in
 
     // Sequence-parallel use: key/value segment i may still be on its way into this GPU's memory
-    // when the kernel starts (a copy engine is bringing it over NVLink). When kv_ready[i] is not
-    // null the TMA producer waits, bounded, until that word equals kv_ready_value before it
-    // touches the segment. The word is written after the copy, in stream order, by the copying
-    // stream. Null for data that is already in place.
+    // when the kernel starts (a copy engine is bringing it over NVLink, one group of
+    // kv_ready_heads_per_group heads at a time). When kv_ready[i] is not null the TMA producer of
+    // a CTA working on head h waits, bounded, until the word kv_ready[i][h / heads_per_group]
+    // equals kv_ready_value before it touches the segment. The word is written after the copy,
+    // in stream order, by the copying stream. Null for data that is already in place.
     const unsigned int* kv_ready[kMaxKvSeg];
     unsigned int        kv_ready_value;
+    int                 kv_ready_heads_per_group;
 };
 
 }  // namespace f2k

@@ -195,6 +195,9 @@ int f2k_attn_create(const f2k_attn_config* cfg, f2k_attn** out) {
     if (e != cudaSuccess) return fail_cuda(h, "cudaDeviceGetAttribute", e);
     if (major != 10)
         return fail(h, F2K_ERR_UNSUPPORTED, "this library contains sm_100a code only (needs a B200-class GPU)");
+    e = attn_fwd_prepare();          // load the kernels now rather than inside the first forward call
+    if (e == cudaSuccess) e = qk_prologue_prepare();
+    if (e != cudaSuccess) return fail_cuda(h, "kernel load", e);
     e = cudaMalloc(reinterpret_cast<void**>(&h->d_status), kStatusBytes);
     if (e != cudaSuccess) return fail_cuda(h, "cudaMalloc(status)", e);
     e = cudaMemset(h->d_status, 0, kStatusBytes);

@@ -260,6 +260,13 @@ int grid_for(long long units, int units_per_block) {
 
 }  // namespace
 
+cudaError_t qk_prologue_prepare() {
+    cudaFuncAttributes attr;
+    cudaError_t e = cudaFuncGetAttributes(&attr, qk_prologue_kernel<4>);
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&attr, qk_prologue_kernel<1>);
+    return e;
+}
+
 cudaError_t qk_prologue_launch(const QkPrologueParams& p, cudaStream_t stream) {
     const long long total = p.row_start[p.n_jobs];
     if (total <= 0) return cudaSuccess;

@@ -5,24 +5,31 @@
 // Tokens are sharded by rank: rank r holds Q, K, V of its `seq_local` tokens. Every rank needs
 // every other rank's K and V. Each rank owns ONE device allocation:
 //
-//     [2 sets][world slots] K shards | [2 sets][world slots] V shards | [2 sets][world] arrival words
+//     [2 sets][world slots] K shards | [2 sets][world slots] V shards | control words
 //
 // A rank writes its own normalised K and its V into slot `rank` of the current set (the set
-// alternates from call to call). After a cross-rank barrier (the host's job: every rank's slot
-// is written), forward() pulls slot p of rank p's allocation into slot p of the local one for
-// every other rank p, in ring order rank+1, rank+2, ..., with the COPY ENGINES
-// (cudaMemcpyAsync through a peer mapping, no SMs), and after each pull writes the arrival word
-// of that slot with a stream memory operation. The attention kernel is launched at once on the
-// compute stream with one key/value segment per rank: its own first, then the others in the
-// order they arrive; its TMA producer waits (bounded) on a segment's arrival word before the
-// first tile of that segment. So the transfer of shard i+1 overlaps the MMAs on shard i, remote
-// data is only ever read from local memory by ordinary single-CTA TMA loads, and nothing waits on
-// another kernel. With overlap off the compute stream simply waits for all pulls.
+// alternates from call to call) and calls forward(). No collective runs inside a step:
 //
-// Two sets: a rank may start writing the next call's K/V while slower peers still pull the
-// current set. The barrier of call n+1 comes after every rank's attention kernel of call n (in
-// stream order), and that kernel cannot finish before its pulls have landed, so set n is free
-// again when call n+2 writes it.
+//  * forward() launches the attention kernel at once on the compute stream, with one key/value
+//    segment per rank: its own first, then rank+1, rank+2, ... The kernel needs nothing remote
+//    for its first segment.
+//  * On the copy stream the rank tells every peer "my slot of this set is written" (a 4-byte
+//    peer copy into the peer's allocation), then, peer by peer in the same ring order, waits for
+//    that peer's word (a stream wait on local memory), pulls the peer's slot into its own
+//    allocation with the COPY ENGINES (2-D peer copies, no SMs) and writes an arrival word.
+//  * Pulls go head group by head group (all peers for the heads of the first wave of CTAs, then
+//    the next wave's heads): CTAs are dispatched head-major, so what a CTA needs arrives before
+//    it gets there, and the transfer of a shard overlaps the MMAs on the shard before it.
+//  * The kernel's TMA producer waits (bounded) on the arrival word of (segment, head group)
+//    before the first tile of a remote segment. Remote data is only ever read from local
+//    memory by ordinary single-CTA TMA loads, and nothing waits on another kernel.
+//
+// With overlap off the compute stream waits for all pulls before the kernel starts.
+//
+// Two sets: a rank may write the next call's K/V while slower peers still pull the current set.
+// A peer's "written" word for call n+1 is sent after its kernel of call n (stream order), and a
+// kernel cannot finish before its pulls have landed, so when this rank's kernel of call n+1 is
+// done every peer has finished pulling set n from it, and call n+2 may overwrite it.
 
 #include "f2k_attn.h"
 
@@ -62,6 +69,11 @@ struct f2k_seqpar {
     std::string err;
     unsigned char* buf = nullptr;       // the allocation described above
     size_t shard_bytes = 0, set_bytes = 0, total_bytes = 0, flags_off = 0;
+    using WaitValue32Fn = CUresult (*)(CUstream, CUdeviceptr, cuuint32_t, unsigned int);
+    WaitValue32Fn wait32 = nullptr;
+    cudaEvent_t written = nullptr;      // compute stream -> copy stream: this rank's K/V are in place
+    cudaStream_t own_copy_stream = nullptr;   // used when the caller passes no copy stream
+    static constexpr int kMaxGroups = 8;
     int*   d_status = nullptr;
     std::vector<unsigned char*> peer;   // base of every rank's allocation as mapped here
     unsigned int epoch = 0;             // call counter; arrival words carry it
@@ -75,8 +87,21 @@ struct f2k_seqpar {
     unsigned char* v_slot(unsigned char* base, int set, int slot) const {
         return base + 2 * set_bytes + ((size_t)set * cfg.world + slot) * shard_bytes;
     }
-    unsigned int* flag(int set, int slot) const {
-        return reinterpret_cast<unsigned int*>(buf + flags_off) + set * cfg.world + slot;
+    // control words (uint32), all inside this rank's allocation so that peers can reach them:
+    //   arrival[set][slot][group]  written locally after a pull        (2 * world * 8 words)
+    //   ready[set][peer]           written by `peer` into THIS buffer  (2 * world words)
+    //   epoch_word                 source of the 4-byte "written" copies (1 word)
+    unsigned int* arrival(int set, int slot) const {
+        return reinterpret_cast<unsigned int*>(buf + flags_off) + ((size_t)set * cfg.world + slot) * kMaxGroups;
+    }
+    static size_t ready_index(int world, int set, int peer) {
+        return (size_t)2 * world * kMaxGroups + (size_t)set * world + peer;
+    }
+    unsigned int* ready(unsigned char* base, int set, int peer) const {
+        return reinterpret_cast<unsigned int*>(base + flags_off) + ready_index(cfg.world, set, peer);
+    }
+    unsigned int* epoch_word() const {
+        return reinterpret_cast<unsigned int*>(buf + flags_off) + (size_t)2 * cfg.world * kMaxGroups + (size_t)2 * cfg.world;
     }
 };
 
@@ -120,7 +145,8 @@ int f2k_seqpar_create(const f2k_seqpar_config* cfg, f2k_seqpar** out) {
     h->shard_bytes = align_up((size_t)cfg->batch * cfg->seq_local * cfg->n_heads * kHeadDim * 2, kAlign);
     h->set_bytes   = (size_t)cfg->world * h->shard_bytes;
     h->flags_off   = 4 * h->set_bytes;
-    h->total_bytes = h->flags_off + align_up((size_t)2 * cfg->world * sizeof(unsigned int), kAlign);
+    h->total_bytes = h->flags_off +
+                     align_up(((size_t)2 * cfg->world * (f2k_seqpar::kMaxGroups + 1) + 1) * sizeof(unsigned int), kAlign);
 
     int dev = 0, major = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -130,7 +156,11 @@ int f2k_seqpar_create(const f2k_seqpar_config* cfg, f2k_seqpar** out) {
     if (major != 10) return fail(h, F2K_ERR_UNSUPPORTED, "this library contains sm_100a code only");
     h->encode  = reinterpret_cast<EncodeTiledFn>(driver_fn("cuTensorMapEncodeTiled"));
     h->write32 = reinterpret_cast<WriteValue32Fn>(driver_fn("cuStreamWriteValue32"));
-    if (!h->encode || !h->write32) return fail(h, F2K_ERR_CUDA, "driver entry points unavailable");
+    h->wait32  = reinterpret_cast<f2k_seqpar::WaitValue32Fn>(driver_fn("cuStreamWaitValue32"));
+    if (!h->encode || !h->write32 || !h->wait32) return fail(h, F2K_ERR_CUDA, "driver entry points unavailable");
+    e = attn_fwd_prepare();           // code is loaded now, never under a pending stream wait
+    if (e == cudaSuccess) e = qk_prologue_prepare();
+    if (e != cudaSuccess) return fail_cuda(h, "kernel load", e);
     e = cudaMalloc(reinterpret_cast<void**>(&h->buf), h->total_bytes);
     if (e != cudaSuccess) return fail_cuda(h, "cudaMalloc(shards)", e);
     e = cudaMemset(h->buf + h->flags_off, 0, h->total_bytes - h->flags_off);
@@ -139,7 +169,9 @@ int f2k_seqpar_create(const f2k_seqpar_config* cfg, f2k_seqpar** out) {
     if (e == cudaSuccess) e = cudaMemset(h->d_status, 0, 256);
     if (e != cudaSuccess) return fail_cuda(h, "cudaMalloc(status)", e);
     e = cudaEventCreateWithFlags(&h->pulled, cudaEventDisableTiming);
-    if (e != cudaSuccess) return fail_cuda(h, "cudaEventCreate", e);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->written, cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&h->own_copy_stream, cudaStreamNonBlocking);
+    if (e != cudaSuccess) return fail_cuda(h, "cudaEventCreate/cudaStreamCreate", e);
     h->peer.assign(cfg->world, nullptr);
     h->peer[cfg->rank] = h->buf;
     h->valid = true;
@@ -149,6 +181,8 @@ int f2k_seqpar_create(const f2k_seqpar_config* cfg, f2k_seqpar** out) {
 void f2k_seqpar_destroy(f2k_seqpar* h) {
     if (!h) return;
     if (h->pulled) cudaEventDestroy(h->pulled);
+    if (h->written) cudaEventDestroy(h->written);
+    if (h->own_copy_stream) cudaStreamDestroy(h->own_copy_stream);
     if (h->d_status) cudaFree(h->d_status);
     if (h->buf) cudaFree(h->buf);
     delete h;
@@ -191,7 +225,7 @@ int f2k_seqpar_forward(f2k_seqpar* h, const void* q_local, void* o_local, int ov
     h->epoch += 1;
     const int set = h->epoch & 1;
     cudaStream_t cs = static_cast<cudaStream_t>(compute_stream);
-    cudaStream_t ps = static_cast<cudaStream_t>(copy_stream);
+    cudaStream_t ps = copy_stream ? static_cast<cudaStream_t>(copy_stream) : h->own_copy_stream;
     if (c.world > 1 && ps == cs && overlap)
         return fail(h, F2K_ERR_INVALID, "overlap needs a copy stream different from the compute stream");
 
@@ -209,44 +243,99 @@ int f2k_seqpar_forward(f2k_seqpar* h, const void* q_local, void* o_local, int ov
     p.n_qseg = 1;
     p.n_q_tiles = tiles_per_seg;
 
-    // pulls in ring order; key/value segment i of the kernel is rank (rank + i) % world
+    // Head groups: as many as the kernel has waves of CTAs (a power of two that divides the head
+    // count, at most 8), so that the heads of the first wave arrive first.
+    int groups = 1;
+    if (overlap && c.world > 1) {
+        int sms = 148;
+        int dev = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        const long long ctas = (long long)((tiles_per_seg + 1) / 2) * c.n_heads * c.batch;
+        const long long waves = (ctas + sms - 1) / sms;
+        while (groups < waves && groups < f2k_seqpar::kMaxGroups && c.n_heads % (groups * 2) == 0) groups *= 2;
+    }
+    const int hpg = c.n_heads / groups;
+
+    // key/value segment i of the kernel is rank (rank + i) % world
     for (int i = 0; i < c.world; ++i) {
         const int src = (c.rank + i) % c.world;
-        unsigned char* k_dst = h->k_slot(h->buf, set, src);
-        unsigned char* v_dst = h->v_slot(h->buf, set, src);
-        if (i > 0) {
-            cudaError_t e = cudaMemcpyAsync(k_dst, h->k_slot(h->peer[src], set, src), h->shard_bytes,
-                                            cudaMemcpyDeviceToDevice, ps);
-            if (e == cudaSuccess)
-                e = cudaMemcpyAsync(v_dst, h->v_slot(h->peer[src], set, src), h->shard_bytes,
-                                    cudaMemcpyDeviceToDevice, ps);
-            if (e != cudaSuccess) return fail_cuda(h, "peer copy", e);
-            if (h->write32(reinterpret_cast<CUstream>(ps), reinterpret_cast<CUdeviceptr>(h->flag(set, src)),
-                           h->epoch, 0) != CUDA_SUCCESS)
-                return fail(h, F2K_ERR_CUDA, "cuStreamWriteValue32 failed");
-            p.kv_ready[i] = overlap ? h->flag(set, src) : nullptr;
-        }
-        if (!encode(h, &p.tm_k[i], k_dst, c.seq_local) || !encode(h, &p.tm_v[i], v_dst, c.seq_local))
+        if (!encode(h, &p.tm_k[i], h->k_slot(h->buf, set, src), c.seq_local) ||
+            !encode(h, &p.tm_v[i], h->v_slot(h->buf, set, src), c.seq_local))
             return fail(h, F2K_ERR_CUDA, "tensor map (K/V) failed");
         p.kv_len[i] = c.seq_local;
         p.kv_tile_start[i] = i * tiles_per_seg;
+        if (i > 0 && overlap) p.kv_ready[i] = h->arrival(set, src);
     }
     p.kv_tile_start[c.world] = c.world * tiles_per_seg;
     p.n_kvseg = c.world;
     p.n_kv_tiles = c.world * tiles_per_seg;
     p.kv_ready_value = h->epoch;
+    p.kv_ready_heads_per_group = hpg;
     p.n_heads = c.n_heads;
     p.batch = c.batch;
     p.scale_log2 = h->scale * 1.4426950408889634f;
     p.status = h->d_status;
 
-    if (c.world > 1 && !overlap) {
-        cudaError_t e = cudaEventRecord(h->pulled, ps);
-        if (e == cudaSuccess) e = cudaStreamWaitEvent(cs, h->pulled, 0);
-        if (e != cudaSuccess) return fail_cuda(h, "event", e);
+    if (c.world > 1) {
+        const cudaError_t we = cudaEventRecord(h->written, cs);   // everything before this call on cs: K/V written
+        if (we != cudaSuccess) return fail_cuda(h, "event", we);
     }
-    const cudaError_t e = attn_fwd_launch(p, cs);
-    if (e != cudaSuccess) return fail_cuda(h, "attention launch", e);
+    // With overlap the kernel goes first: its first segment is local, and the host then queues
+    // the pulls while the kernel is already running.
+    bool launched = false;
+    if (overlap || c.world == 1) {
+        const cudaError_t le = attn_fwd_launch(p, cs);
+        if (le != cudaSuccess) return fail_cuda(h, "attention launch", le);
+        launched = true;
+    }
+    if (c.world > 1) {
+        // (1) the copy stream may go once this rank's K/V are in place (event recorded above,
+        //     before the kernel launch)
+        cudaError_t e = cudaStreamWaitEvent(ps, h->written, 0);
+        if (e != cudaSuccess) return fail_cuda(h, "event", e);
+        // (2) tell every peer (a 4-byte copy of the call number into the peer's allocation)
+        if (h->write32(reinterpret_cast<CUstream>(ps), reinterpret_cast<CUdeviceptr>(h->epoch_word()), h->epoch, 0) != CUDA_SUCCESS)
+            return fail(h, F2K_ERR_CUDA, "cuStreamWriteValue32 failed");
+        for (int i = 1; i < c.world; ++i) {
+            const int dstr = (c.rank + i) % c.world;
+            e = cudaMemcpyAsync(h->ready(h->peer[dstr], set, c.rank), h->epoch_word(), sizeof(unsigned int),
+                                cudaMemcpyDeviceToDevice, ps);
+            if (e != cudaSuccess) return fail_cuda(h, "peer notify", e);
+        }
+        // (3) pulls: head group by head group, peers in ring order
+        const size_t pitch = (size_t)c.n_heads * kHeadDim * 2;
+        const size_t width = (size_t)hpg * kHeadDim * 2;
+        const size_t rows  = (size_t)c.batch * c.seq_local;
+        for (int g = 0; g < groups; ++g) {
+            for (int i = 1; i < c.world; ++i) {
+                const int src = (c.rank + i) % c.world;
+                if (g == 0 &&
+                    h->wait32(reinterpret_cast<CUstream>(ps), reinterpret_cast<CUdeviceptr>(h->ready(h->buf, set, src)),
+                              h->epoch, 0 /* CU_STREAM_WAIT_VALUE_GEQ */) != CUDA_SUCCESS)
+                    return fail(h, F2K_ERR_CUDA, "cuStreamWaitValue32 failed");
+                const size_t off = (size_t)g * width;
+                e = cudaMemcpy2DAsync(h->k_slot(h->buf, set, src) + off, pitch, h->k_slot(h->peer[src], set, src) + off,
+                                      pitch, width, rows, cudaMemcpyDeviceToDevice, ps);
+                if (e == cudaSuccess)
+                    e = cudaMemcpy2DAsync(h->v_slot(h->buf, set, src) + off, pitch,
+                                          h->v_slot(h->peer[src], set, src) + off, pitch, width, rows,
+                                          cudaMemcpyDeviceToDevice, ps);
+                if (e != cudaSuccess) return fail_cuda(h, "peer copy", e);
+                if (h->write32(reinterpret_cast<CUstream>(ps), reinterpret_cast<CUdeviceptr>(h->arrival(set, src) + g),
+                               h->epoch, 0) != CUDA_SUCCESS)
+                    return fail(h, F2K_ERR_CUDA, "cuStreamWriteValue32 failed");
+            }
+        }
+        if (!overlap) {
+            e = cudaEventRecord(h->pulled, ps);
+            if (e == cudaSuccess) e = cudaStreamWaitEvent(cs, h->pulled, 0);
+            if (e != cudaSuccess) return fail_cuda(h, "event", e);
+        }
+    }
+    if (!launched) {
+        const cudaError_t le = attn_fwd_launch(p, cs);
+        if (le != cudaSuccess) return fail_cuda(h, "attention launch", le);
+    }
     return F2K_OK;
 }
 

@@ -4,9 +4,9 @@ One process per GPU. Rank r holds the queries, keys and values of its `seq_local
 text||image sequence; `SequenceParallelAttention.forward` gives it the attention output of its
 queries over every rank's keys and values. The K/V shards of the other ranks are pulled into
 local memory by the copy engines over NVLink while the attention kernel already works on what
-has arrived (see csrc/seqpar.cu). torch.distributed is used for two things only: handing the
-64-byte IPC handles of the shard buffers around once, and one tiny all-reduce per step as the
-"every rank's K/V is written" barrier.
+has arrived (see csrc/seqpar.cu). torch.distributed is used once, to hand the 64-byte IPC handles
+of the shard buffers around; a step runs no collective (the ranks tell each other "my K/V are
+written" through words in those buffers).
 
 `plan_ring` and `shard_bounds` are pure host logic (tested on CPU with gloo ranks).
 """
@@ -47,7 +47,6 @@ class SequenceParallelAttention:
         cfg = SeqParConfig(batch, seq_local, n_heads, head_dim, world, rank, scale)
         self._rc = lib.f2k_seqpar_create(C.byref(cfg), C.byref(self._h))
         self._opened = []
-        self._copy_stream = None
 
     def __del__(self):
         if lib is None:          # interpreter shutdown
@@ -104,17 +103,13 @@ class SequenceParallelAttention:
         return _tensor_from_ptr(k.value, shape), _tensor_from_ptr(v.value, shape)
 
     def forward(self, q_local, o_local, overlap: bool = True, stream=None) -> bool:
+        """Attention of this rank's queries over all ranks' keys/values. `stream` is the compute
+        stream this rank wrote its K/V on; the pulls run on a copy stream owned by the handle."""
         import torch
         if stream is None:
             stream = torch.cuda.current_stream()
-        if self._copy_stream is None:
-            self._copy_stream = torch.cuda.Stream()
-        # pulls may start once everything queued so far on the compute stream is done (the
-        # caller's K/V writes and the cross-rank barrier)
-        self._copy_stream.wait_stream(stream)
         rc = lib.f2k_seqpar_forward(self._h, C.c_void_p(q_local.data_ptr()), C.c_void_p(o_local.data_ptr()),
-                                    int(overlap), C.c_void_p(stream.cuda_stream),
-                                    C.c_void_p(self._copy_stream.cuda_stream))
+                                    int(overlap), C.c_void_p(stream.cuda_stream), None)
         return rc == _lib.F2K_OK
 
     def device_status(self) -> int:

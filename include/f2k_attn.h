@@ -173,9 +173,9 @@ int f2k_build_rope_4axis_tables(const int* axes_dim, int n_axes,
  * sharded by rank (one process per GPU); every rank attends its seq_local queries to the keys
  * and values of all ranks. Remote K/V shards are pulled into local memory by the copy engines
  * over NVLink while the attention kernel already works on the shards that have arrived.
- * Call order per step: write this rank's normalised K and its V to the pointers given by
- * f2k_seqpar_local_kv -> cross-rank barrier (the host's job, e.g. an all-reduce on the compute
- * stream) -> f2k_seqpar_forward. */
+ * Call order per step: write this rank's normalised K and its V (on the compute stream) to the
+ * pointers given by f2k_seqpar_local_kv, then f2k_seqpar_forward. No collective is needed: the
+ * ranks announce "written" to each other through words in their shard buffers. */
 typedef struct f2k_seqpar f2k_seqpar; /* opaque */
 
 typedef struct f2k_seqpar_config {
@@ -200,7 +200,8 @@ int f2k_seqpar_attach(f2k_seqpar* h, void* const* peer_bases);
 /* Where this rank's K (normalised, rotated) and V for the next forward call have to be written. */
 int f2k_seqpar_local_kv(f2k_seqpar* h, void** k, void** v);
 /* q_local, o_local: [batch, seq_local, n_heads, 128] bf16. overlap != 0: the kernel starts at
- * once and waits per shard for its arrival; overlap == 0: it starts after all pulls. */
+ * once and waits per shard for its arrival; overlap == 0: it starts after all pulls.
+ * copy_stream NULL selects a stream the handle owns (it must differ from compute_stream). */
 int f2k_seqpar_forward(f2k_seqpar* h, const void* q_local, void* o_local, int overlap,
                        void* compute_stream, void* copy_stream);
 int f2k_seqpar_device_status(f2k_seqpar* h, int* status_out);

@@ -27,11 +27,10 @@ def main():
     assert sp.ok(), sp.last_error()
     assert sp.attach_distributed(), sp.last_error()
     dq = dev_bf16(q[:, b:e])
-    token = torch.ones(1, device="cuda")
     for step, overlap in enumerate((True, False, True)):
         ks, vs = sp.local_kv()
         ks.copy_(dev_bf16(k[:, b:e])); vs.copy_(dev_bf16(v[:, b:e]))
-        dist.all_reduce(token, op=dist.ReduceOp.MAX)                  # every rank's K/V is written (stream-ordered)
+        # no collective here: readiness travels as words in the shard buffers
         do = torch.full_like(dq, float("nan"))
         assert sp.forward(dq, do, overlap=overlap), sp.last_error()
         torch.cuda.synchronize()

@@ -22,8 +22,22 @@ pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
 
 
+_STREAMS = []
+
+
+def _rank_streams(world):
+    """Eight distinct streams, made once: torch hands streams out of a small pool round-robin, and
+    two ranks must never end up on the same underlying stream."""
+    import torch
+    while len(_STREAMS) < 8:
+        _STREAMS.append(torch.cuda.Stream())
+    assert len({s.cuda_stream for s in _STREAMS}) == 8
+    return _STREAMS[:world]
+
+
 @pytest.mark.parametrize("world,per,H,B,overlap", [(2, 256, 4, 1, True), (4, 200, 2, 1, True), (4, 200, 2, 1, False),
                                                    (8, 136, 2, 2, True), (3, 128, 1, 1, True), (1, 300, 2, 1, True)])
+@pytest.mark.timeout(120, method="thread")      # a stream wait that never ends must end the run
 def test_all_ranks_in_one_process(orc, world, per, H, B, overlap):
     import torch
     from f2k_cuda_b200.seqpar import SequenceParallelAttention, shard_bounds
@@ -35,19 +49,20 @@ def test_all_ranks_in_one_process(orc, world, per, H, B, overlap):
         assert r.ok(), r.last_error()
     for r in ranks:
         assert r.attach_in_process(ranks)
+    streams = _rank_streams(world)              # every rank has its own compute stream
     for step in range(2):                       # twice: both buffer sets, fresh arrival values
         outs = []
+        for r, sp in enumerate(ranks):          # every rank's inputs first (ranks share this GPU:
+            b, e = shard_bounds(S, world, r)    # a rank's kernel must never wait for SM work of another)
+            with torch.cuda.stream(streams[r]):
+                ks, vs = sp.local_kv()
+                ks.copy_(dev_bf16(k[:, b:e])); vs.copy_(dev_bf16(v[:, b:e]))
+                dq = dev_bf16(q[:, b:e])
+                outs.append((dq, torch.full_like(dq, float("nan"))))
+        torch.cuda.synchronize()
         for r, sp in enumerate(ranks):
-            b, e = shard_bounds(S, world, r)
-            ks, vs = sp.local_kv()
-            ks.copy_(dev_bf16(k[:, b:e])); vs.copy_(dev_bf16(v[:, b:e]))
-        torch.cuda.synchronize()                # stands in for the cross-rank barrier
-        for r, sp in enumerate(ranks):
-            b, e = shard_bounds(S, world, r)
-            dq = dev_bf16(q[:, b:e])
-            do = torch.full_like(dq, float("nan"))
-            assert sp.forward(dq, do, overlap=overlap), sp.last_error()
-            outs.append((dq, do))
+            # no barrier between the ranks: they tell each other through words in their shard buffers
+            assert sp.forward(outs[r][0], outs[r][1], overlap=overlap, stream=streams[r]), sp.last_error()
         torch.cuda.synchronize()
         for r, sp in enumerate(ranks):
             assert sp.device_status() == 0, sp.last_error()
