@@ -14,8 +14,13 @@ torchrun): batch N with the 32 heads sharded 32/N per GPU, so every GPU still ow
 `value` is device-timed with inputs resident in HBM; `e2e` is the same step through the
 host-buffer entry point with pinned host tensors (H2D of Q, K, V and D2H of O inside the
 timed region). `roofline` times the attention kernel alone. `cpu_baseline` is the fp32 host
-restatement (oracle/) on a bounded head sample. `--impl reference` runs the reference's own
-CUDA kernels rebuilt for sm_100a (oracle/_ref) on the same workload.
+restatement (oracle/) on a bounded head sample; `reference_kernel` is a short run of the
+reference's own CUDA kernels, rebuilt for sm_100a (oracle/_ref), on the same GPU in the same
+run. `--impl reference` runs those kernels as the whole measurement on the same workload.
+
+Other workloads (--workload): the long shapes with the sequence sharded over the GPUs
+(*_seqpar) or with the heads sharded (*_heads), and the batch-4 step with heads sharded; these
+are strong-scaling jobs and print the same line without the roofline, e2e and CPU legs.
 """
 from __future__ import annotations
 
@@ -24,7 +29,6 @@ import ctypes as C
 import json
 import os
 import statistics
-import subprocess
 import sys
 import time
 from pathlib import Path
@@ -50,11 +54,15 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="s4608", choices=["s4608", "s8704_seqpar", "s16896_seqpar"],
-                    help="s4608: the headline shape (heads sharded over the GPUs). *_seqpar: the long shapes with the "
-                         "sequence sharded over the GPUs (strong scaling, K/V pulled over NVLink under the kernel)")
+    ap.add_argument("--workload", default="s4608",
+                    choices=["s4608", "s8704_seqpar", "s16896_seqpar", "s4608_b4_heads", "s8704_heads", "s16896_heads"],
+                    help="s4608: the headline shape (heads sharded over the GPUs, batch grows with N). *_seqpar: the "
+                         "long shapes with the sequence sharded over the GPUs (strong scaling, K/V pulled over NVLink "
+                         "under the kernel). *_heads: a fixed job with its 32 heads sharded 32/N per GPU (strong scaling)")
     ap.add_argument("--no-overlap", action="store_true", help="seqpar: start the kernel only after all K/V pulls")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the timed CPU leg")
+    ap.add_argument("--no-reference-kernel", action="store_true",
+                    help="skip the short leg that times the reference's rebuilt kernels beside ours (N = 1)")
     ap.add_argument("--skip-e2e", action="store_true",
                     help="skip the host-buffer leg (for short profiler captures; the line then has e2e null)")
     return ap.parse_args()
@@ -72,51 +80,54 @@ def measured_peak():
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons sampled while the timed regions run."""
-    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
-         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-         "clocks_event_reasons.sw_power_cap")
+    """SM clock and throttle reasons of one GPU, read through NVML every few milliseconds by a
+    thread of this process while the timed regions run (reading only; nothing is set)."""
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown"}
 
-    def __init__(self, device: int):
-        self.proc = None
+    def __init__(self, device: int, period_s: float = 0.004):
+        import threading
+        self.samples, self.mask, self.max_mhz, self.err = [], 0, None, None
+        self._stop = threading.Event()
+        self._thread = None
         try:
+            import pynvml
+            pynvml.nvmlInit()
             uuid = str(torch.cuda.get_device_properties(device).uuid)
             if not uuid.startswith("GPU-"):
                 uuid = "GPU-" + uuid
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", uuid, f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100"],
-                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-        except Exception:
-            self.proc = None
+            try:
+                h = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+            except Exception:
+                h = pynvml.nvmlDeviceGetHandleByUUID(uuid)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM))
+            reasons = getattr(pynvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+                pynvml.nvmlDeviceGetCurrentClocksThrottleReasons
+
+            def poll():
+                while not self._stop.is_set():
+                    try:
+                        self.samples.append(float(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)))
+                        self.mask |= int(reasons(h))
+                    except Exception as exc:
+                        self.err = str(exc)
+                        return
+                    time.sleep(period_s)
+
+            self._thread = threading.Thread(target=poll, daemon=True)
+            self._thread.start()
+        except Exception as exc:
+            self.err = f"NVML unavailable: {exc}"
 
     def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            out, _ = self.proc.communicate(timeout=5)
-        except Exception:
-            self.proc.kill()
-            out = ""
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in out.strip().splitlines():
-            parts = [x.strip() for x in line.split(",")]
-            if len(parts) < 7:
-                continue
-            try:
-                sm.append(float(parts[0])); mx.append(float(parts[1]))
-            except ValueError:
-                continue
-            for n, v in zip(names, parts[3:7]):
-                if v.lower().startswith("active"):
-                    reasons.add(n)
-        if not sm:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
-        top = max(sm)
-        load = [x for x in sm if x >= 0.6 * top]       # samples taken while kernels ran
-        return {"sm_mhz": statistics.median(load), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
-                "samples": len(sm)}
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=2)
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [self.err or "no samples"]}
+        top = max(self.samples)
+        load = [x for x in self.samples if x >= 0.6 * top]       # samples taken while kernels ran
+        return {"sm_mhz": statistics.median(load), "sm_min_mhz": min(load), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(n for bit, n in self.REASONS.items() if self.mask & bit), "samples": len(self.samples)}
 
 
 def dev_bf16(bits):
@@ -292,6 +303,19 @@ def run_ours(args, rank, world):
     }
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(p, tabs, flops / H)
+    if world == 1 and not args.no_reference_kernel:
+        # the reference's own kernels, rebuilt for sm_100a, in this same run on this same GPU
+        import copy
+        a = copy.copy(args)
+        a.steps, a.warmup = 5, 3
+        try:
+            r = run_reference(a, 0, 1)
+        except Exception as exc:  # the comparison leg must not take the measurement down with it
+            r = {"unavailable": f"{type(exc).__name__}: {exc}"}
+        line["reference_kernel"] = (
+            {"unavailable": r["unavailable"]} if "unavailable" in r else
+            {"value": r["value"], "unit": UNIT, "ms_per_step": r["ms_per_step"], "e2e_value": r["e2e"]["value"],
+             "steps": a.steps, "what": r["config"]["step"]})
     return line
 
 
@@ -385,6 +409,65 @@ def run_seqpar(args, rank, world):
         "per_gpu_tflops": flops / world / (ms * 1e-3) / 1e12,
         "pct_of_peak": 100.0 * flops / world / (ms * 1e-3) / 1e12 / peak, "peak_source": peak_src,
         "e2e": None, "gpu_launches": (4 if 0 < n_txt < per else 2) * args.steps + args.steps, "clocks": clocks,
+    }
+
+
+def run_heads_strong(args, rank, world):
+    """A fixed job (batch-4 1024px step, image-edit shape or 2048px shape) with its 32 heads sharded
+    32/N per GPU: strong scaling, no traffic between the GPUs inside the step. Inputs are drawn on
+    the device (N(0,1), seeded per rank); gains and RoPE tables as in the headline workload."""
+    import f2k_cuda_b200 as f2k
+    from f2k_cuda_b200.inputs import WORKLOADS, make_problem, token_positions
+    w = WORKLOADS[{"s4608_b4_heads": "s4608_b4", "s8704_heads": "s8704_edit", "s16896_heads": "s16896"}[args.workload]]
+    B, St, Si, D = w.batch, w.seq_txt, w.seq_img, w.head_dim
+    H = w.n_heads // world
+    stream = torch.cuda.current_stream()
+    pt, pi = token_positions(w)
+    dtab = [torch.from_numpy(t).cuda() for t in (*f2k.build_rope_4axis_tables((32,) * 4, pt, 2000.0),
+                                                 *f2k.build_rope_4axis_tables((32,) * 4, pi, 2000.0))]
+    dg = [dev_bf16(g) for g in make_problem(WORKLOADS["s1152"], heads=1).gammas]
+    gen = torch.Generator(device="cuda").manual_seed(4321 + rank)
+    mk = lambda n: torch.randn(B, n, H, D, device="cuda", generator=gen).to(torch.bfloat16)  # noqa: E731
+    d = [mk(St), mk(St), mk(St), mk(Si), mk(Si), mk(Si)]
+    ja = f2k.JointAttention(f2k.JointAttention.Config(B, St, Si, H, D))
+    if not ja.ok():
+        raise RuntimeError(ja.last_error())
+    o_t, o_i = torch.empty_like(d[0]), torch.empty_like(d[3])
+    ws = torch.empty(ja.fused_workspace_size_bytes(), dtype=torch.uint8, device="cuda")
+
+    def step():
+        if not ja.forward_fused(*d, dg, dtab, 1e-6, o_t, o_i, ws):
+            raise RuntimeError(ja.last_error())
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    sampler = ClockSampler(torch.cuda.current_device()) if rank == 0 else None
+    if world > 1:
+        torch.distributed.barrier()
+    ms = time_region(step, args.steps, stream)
+    if world > 1:
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        ms = float(t.item())
+    clocks = sampler.stop() if sampler else None
+    if ja.device_status() != 0:
+        raise RuntimeError("attention kernel reported a device-side error")
+    if rank != 0:
+        return None
+    flops = 4.0 * B * w.n_heads * float(St + Si) ** 2 * D      # whole job
+    peak, peak_src = measured_peak()
+    return {
+        "metric": METRIC, "value": flops / (ms * 1e-3) / 1e12, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"{w.name}: {St + Si} tokens, batch {B}, hd128, 32 heads sharded {H} per GPU",
+                   "step": "fused QK-RMSNorm + 4-axis RoPE + non-causal attention, one call",
+                   "flops_per_step_total": flops, "parallelism": f"heads{world}" if world > 1 else "single",
+                   "l2": "Q, K, V, O and workspace of a step (%.0f MB per GPU) exceed the 126 MB L2"
+                         % (6 * B * (St + Si) * H * D * 2 / 1e6)},
+        "per_gpu_tflops": flops / world / (ms * 1e-3) / 1e12,
+        "pct_of_peak": 100.0 * flops / world / (ms * 1e-3) / 1e12 / peak, "peak_source": peak_src,
+        "e2e": None, "gpu_launches": 2 * args.steps, "clocks": clocks,
     }
 
 
@@ -516,6 +599,8 @@ def main():
             line = run_reference(args, rank, world)
         elif args.workload == "s4608":
             line = run_ours(args, rank, world)
+        elif args.workload.endswith("_heads"):
+            line = run_heads_strong(args, rank, world)
         else:
             line = run_seqpar(args, rank, world)
         if line is not None:

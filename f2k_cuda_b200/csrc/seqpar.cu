@@ -5,7 +5,7 @@
 // Tokens are sharded by rank: rank r holds Q, K, V of its `seq_local` tokens. Every rank needs
 // every other rank's K and V. Each rank owns ONE device allocation:
 //
-//     [2 sets][world slots] K shards | [2 sets][world slots] V shards | control words
+//     [2 sets][world slots] { K shard, V shard } | control words
 //
 // A rank writes its own normalised K and its V into slot `rank` of the current set (the set
 // alternates from call to call) and calls forward(). No collective runs inside a step:
@@ -13,13 +13,16 @@
 //  * forward() launches the attention kernel at once on the compute stream, with one key/value
 //    segment per rank: its own first, then rank+1, rank+2, ... The kernel needs nothing remote
 //    for its first segment.
-//  * On the copy stream the rank tells every peer "my slot of this set is written" (a 4-byte
-//    peer copy into the peer's allocation), then, peer by peer in the same ring order, waits for
-//    that peer's word (a stream wait on local memory), pulls the peer's slot into its own
-//    allocation with the COPY ENGINES (2-D peer copies, no SMs) and writes an arrival word.
-//  * Pulls go head group by head group (all peers for the heads of the first wave of CTAs, then
-//    the next wave's heads): CTAs are dispatched head-major, so what a CTA needs arrives before
-//    it gets there, and the transfer of a shard overlaps the MMAs on the shard before it.
+//  * On the copy stream the rank tells every peer "my slot of this set is written" (a 32-bit
+//    stream write into the peer's allocation), then, peer by peer in the same ring order, waits
+//    for that peer's word (a stream wait on local memory), pulls the peer's slot into its own
+//    allocation with the COPY ENGINES (no SMs) and writes an arrival word. K and V of a slot are
+//    adjacent, so one copy moves both: a copy costs about 10 us on top of its bytes, and copies
+//    of one stream pair do not run side by side, so fewer and larger copies win.
+//  * When the kernel is the longer leg, pulls go head group by head group (all peers for the
+//    heads of the first wave of CTAs, then the next wave's heads; one 3-D copy takes a group's
+//    columns of K and V): CTAs are dispatched head-major, so what a CTA needs arrives before it
+//    gets there. When the transfer is the longer leg a slot moves whole, in one linear copy.
 //  * The kernel's TMA producer waits (bounded) on the arrival word of (segment, head group)
 //    before the first tile of a remote segment. Remote data is only ever read from local
 //    memory by ordinary single-CTA TMA loads, and nothing waits on another kernel.
@@ -37,6 +40,7 @@
 
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <string>
@@ -81,11 +85,12 @@ struct f2k_seqpar {
     EncodeTiledFn  encode = nullptr;
     WriteValue32Fn write32 = nullptr;
 
+    bool peer_write32 = true;           // stream writes straight into a peer's words work here
     unsigned char* k_slot(unsigned char* base, int set, int slot) const {
-        return base + ((size_t)set * cfg.world + slot) * shard_bytes;
+        return base + ((size_t)set * cfg.world + slot) * 2 * shard_bytes;
     }
     unsigned char* v_slot(unsigned char* base, int set, int slot) const {
-        return base + 2 * set_bytes + ((size_t)set * cfg.world + slot) * shard_bytes;
+        return k_slot(base, set, slot) + shard_bytes;      // V directly behind K: one copy moves both
     }
     // control words (uint32), all inside this rank's allocation so that peers can reach them:
     //   arrival[set][slot][group]  written locally after a pull        (2 * world * 8 words)
@@ -142,7 +147,7 @@ int f2k_seqpar_create(const f2k_seqpar_config* cfg, f2k_seqpar** out) {
         return fail(h, F2K_ERR_INVALID, "sequence-parallel attention: world must be 1..8 and 0 <= rank < world");
     if (cfg->head_dim != kHeadDim) return fail(h, F2K_ERR_UNSUPPORTED, "head_dim must be 128");
     h->scale = cfg->scale > 0.f ? cfg->scale : 1.0f / std::sqrt((float)cfg->head_dim);
-    h->shard_bytes = align_up((size_t)cfg->batch * cfg->seq_local * cfg->n_heads * kHeadDim * 2, kAlign);
+    h->shard_bytes = (size_t)cfg->batch * cfg->seq_local * cfg->n_heads * kHeadDim * 2;   // a multiple of 256
     h->set_bytes   = (size_t)cfg->world * h->shard_bytes;
     h->flags_off   = 4 * h->set_bytes;
     h->total_bytes = h->flags_off +
@@ -243,8 +248,9 @@ int f2k_seqpar_forward(f2k_seqpar* h, const void* q_local, void* o_local, int ov
     p.n_qseg = 1;
     p.n_q_tiles = tiles_per_seg;
 
-    // Head groups: as many as the kernel has waves of CTAs (a power of two that divides the head
-    // count, at most 8), so that the heads of the first wave arrive first.
+    // Head groups. If the kernel is clearly the longer leg: as many groups as it has waves of
+    // CTAs (a power of two that divides the head count, at most 8, copies of 8 MB or more), so
+    // that the heads of the first wave arrive first. If the transfer is: whole slots.
     int groups = 1;
     if (overlap && c.world > 1) {
         int sms = 148;
@@ -252,7 +258,17 @@ int f2k_seqpar_forward(f2k_seqpar* h, const void* q_local, void* o_local, int ov
         if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         const long long ctas = (long long)((tiles_per_seg + 1) / 2) * c.n_heads * c.batch;
         const long long waves = (ctas + sms - 1) / sms;
-        while (groups < waves && groups < f2k_seqpar::kMaxGroups && c.n_heads % (groups * 2) == 0) groups *= 2;
+        const double s_all = (double)c.seq_local * c.world;
+        const double t_kernel = 4.0 * c.batch * c.n_heads * c.seq_local * s_all * kHeadDim / 1.1e15;
+        const double t_copy = (c.world - 1) * (2.0 * h->shard_bytes / 7.4e11 + 10e-6);
+        if (t_copy < 0.85 * t_kernel)
+            while (groups < waves && groups < f2k_seqpar::kMaxGroups && c.n_heads % (groups * 2) == 0 &&
+                   2 * h->shard_bytes / (groups * 2) >= ((size_t)8 << 20))
+                groups *= 2;
+        if (const char* env = std::getenv("F2K_SEQPAR_GROUPS")) {       // measurement knob
+            const int g = std::atoi(env);
+            if (g >= 1 && g <= f2k_seqpar::kMaxGroups && c.n_heads % g == 0) groups = g;
+        }
     }
     const int hpg = c.n_heads / groups;
 
@@ -293,16 +309,22 @@ int f2k_seqpar_forward(f2k_seqpar* h, const void* q_local, void* o_local, int ov
         //     before the kernel launch)
         cudaError_t e = cudaStreamWaitEvent(ps, h->written, 0);
         if (e != cudaSuccess) return fail_cuda(h, "event", e);
-        // (2) tell every peer (a 4-byte copy of the call number into the peer's allocation)
+        // (2) tell every peer: the call number goes into the peer's allocation, by a stream write
+        //     where the driver takes a peer address for one, else by a 4-byte copy
         if (h->write32(reinterpret_cast<CUstream>(ps), reinterpret_cast<CUdeviceptr>(h->epoch_word()), h->epoch, 0) != CUDA_SUCCESS)
             return fail(h, F2K_ERR_CUDA, "cuStreamWriteValue32 failed");
         for (int i = 1; i < c.world; ++i) {
             const int dstr = (c.rank + i) % c.world;
-            e = cudaMemcpyAsync(h->ready(h->peer[dstr], set, c.rank), h->epoch_word(), sizeof(unsigned int),
-                                cudaMemcpyDeviceToDevice, ps);
-            if (e != cudaSuccess) return fail_cuda(h, "peer notify", e);
+            unsigned int* word = h->ready(h->peer[dstr], set, c.rank);
+            if (h->peer_write32 &&
+                h->write32(reinterpret_cast<CUstream>(ps), reinterpret_cast<CUdeviceptr>(word), h->epoch, 0) != CUDA_SUCCESS)
+                h->peer_write32 = false;
+            if (!h->peer_write32) {
+                e = cudaMemcpyAsync(word, h->epoch_word(), sizeof(unsigned int), cudaMemcpyDeviceToDevice, ps);
+                if (e != cudaSuccess) return fail_cuda(h, "peer notify", e);
+            }
         }
-        // (3) pulls: head group by head group, peers in ring order
+        // (3) pulls: head group by head group, peers in ring order; K and V in one copy
         const size_t pitch = (size_t)c.n_heads * kHeadDim * 2;
         const size_t width = (size_t)hpg * kHeadDim * 2;
         const size_t rows  = (size_t)c.batch * c.seq_local;
@@ -313,13 +335,20 @@ int f2k_seqpar_forward(f2k_seqpar* h, const void* q_local, void* o_local, int ov
                     h->wait32(reinterpret_cast<CUstream>(ps), reinterpret_cast<CUdeviceptr>(h->ready(h->buf, set, src)),
                               h->epoch, 0 /* CU_STREAM_WAIT_VALUE_GEQ */) != CUDA_SUCCESS)
                     return fail(h, F2K_ERR_CUDA, "cuStreamWaitValue32 failed");
-                const size_t off = (size_t)g * width;
-                e = cudaMemcpy2DAsync(h->k_slot(h->buf, set, src) + off, pitch, h->k_slot(h->peer[src], set, src) + off,
-                                      pitch, width, rows, cudaMemcpyDeviceToDevice, ps);
-                if (e == cudaSuccess)
-                    e = cudaMemcpy2DAsync(h->v_slot(h->buf, set, src) + off, pitch,
-                                          h->v_slot(h->peer[src], set, src) + off, pitch, width, rows,
-                                          cudaMemcpyDeviceToDevice, ps);
+                unsigned char* dst_k = h->k_slot(h->buf, set, src);
+                unsigned char* src_k = h->k_slot(h->peer[src], set, src);
+                if (groups == 1) {
+                    e = cudaMemcpyAsync(dst_k, src_k, 2 * h->shard_bytes, cudaMemcpyDeviceToDevice, ps);
+                } else {
+                    // columns [g * width, (g + 1) * width) of every token row, planes K and V
+                    cudaMemcpy3DParms cp;
+                    std::memset(&cp, 0, sizeof cp);
+                    cp.srcPtr = make_cudaPitchedPtr(src_k + (size_t)g * width, pitch, width, rows);
+                    cp.dstPtr = make_cudaPitchedPtr(dst_k + (size_t)g * width, pitch, width, rows);
+                    cp.extent = make_cudaExtent(width, rows, 2);
+                    cp.kind   = cudaMemcpyDeviceToDevice;
+                    e = cudaMemcpy3DAsync(&cp, ps);
+                }
                 if (e != cudaSuccess) return fail_cuda(h, "peer copy", e);
                 if (h->write32(reinterpret_cast<CUstream>(ps), reinterpret_cast<CUdeviceptr>(h->arrival(set, src) + g),
                                h->epoch, 0) != CUDA_SUCCESS)

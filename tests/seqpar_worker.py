@@ -27,7 +27,12 @@ def main():
     assert sp.ok(), sp.last_error()
     assert sp.attach_distributed(), sp.last_error()
     dq = dev_bf16(q[:, b:e])
-    for step, overlap in enumerate((True, False, True)):
+    # (overlap, head groups a slot is pulled in; 0 = the library's choice)
+    for step, (overlap, groups) in enumerate(((True, 0), (False, 0), (True, 2), (True, 0), (True, 4))):
+        if groups:
+            os.environ["F2K_SEQPAR_GROUPS"] = str(groups)
+        else:
+            os.environ.pop("F2K_SEQPAR_GROUPS", None)
         ks, vs = sp.local_kv()
         ks.copy_(dev_bf16(k[:, b:e])); vs.copy_(dev_bf16(v[:, b:e]))
         # no collective here: readiness travels as words in the shard buffers

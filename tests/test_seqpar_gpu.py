@@ -35,12 +35,20 @@ def _rank_streams(world):
     return _STREAMS[:world]
 
 
-@pytest.mark.parametrize("world,per,H,B,overlap", [(2, 256, 4, 1, True), (4, 200, 2, 1, True), (4, 200, 2, 1, False),
-                                                   (8, 136, 2, 2, True), (3, 128, 1, 1, True), (1, 300, 2, 1, True)])
+# groups: 0 = the library's own choice (whole slots at these sizes), else the number of head
+# groups a slot is pulled in (one 3-D copy per group)
+@pytest.mark.parametrize("world,per,H,B,overlap,groups",
+                         [(2, 256, 4, 1, True, 0), (4, 200, 2, 1, True, 0), (4, 200, 2, 1, False, 0),
+                          (8, 136, 2, 2, True, 0), (3, 128, 1, 1, True, 0), (1, 300, 2, 1, True, 0),
+                          (2, 256, 4, 1, True, 4), (4, 200, 2, 2, True, 2), (8, 136, 8, 1, True, 8)])
 @pytest.mark.timeout(120, method="thread")      # a stream wait that never ends must end the run
-def test_all_ranks_in_one_process(orc, world, per, H, B, overlap):
+def test_all_ranks_in_one_process(orc, monkeypatch, world, per, H, B, overlap, groups):
     import torch
     from f2k_cuda_b200.seqpar import SequenceParallelAttention, shard_bounds
+    if groups:
+        monkeypatch.setenv("F2K_SEQPAR_GROUPS", str(groups))
+    else:
+        monkeypatch.delenv("F2K_SEQPAR_GROUPS", raising=False)
     S, D = world * per, 128
     q, k, v = (normal_bits(0x5E9, i, (B, S, H, D)) for i in range(3))
     _, ref = orc.joint_path(q_img=q, k_img=k, v_img=v)
