@@ -9,6 +9,7 @@
 
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <string>
@@ -87,9 +88,15 @@ struct f2k_attn {
     bool        have_params = false;
     AttnParams  params;
 
-    // Device staging of the host-buffer entry point.
+    // Host-buffer entry point: device staging, and the pipeline that overlaps the transfers of
+    // one head group with the kernels of another (children: one handle per head group, each for
+    // n_heads / groups heads; two extra streams, one per transfer direction).
     void*  stage = nullptr;
     size_t stage_bytes = 0;
+    std::vector<f2k_attn*>   child;
+    std::vector<cudaEvent_t> arrived, computed;
+    cudaStream_t s_in = nullptr, s_out = nullptr;
+    cudaEvent_t  ev_start = nullptr, ev_out = nullptr;
 
     size_t bytes_txt() const {
         return (size_t)cfg.batch * cfg.seq_txt * cfg.n_heads * cfg.head_dim * 2;
@@ -208,6 +215,13 @@ int f2k_attn_create(const f2k_attn_config* cfg, f2k_attn** out) {
 
 void f2k_attn_destroy(f2k_attn* h) {
     if (!h) return;
+    for (f2k_attn* c : h->child) f2k_attn_destroy(c);
+    for (cudaEvent_t e : h->arrived) cudaEventDestroy(e);
+    for (cudaEvent_t e : h->computed) cudaEventDestroy(e);
+    if (h->ev_start) cudaEventDestroy(h->ev_start);
+    if (h->ev_out) cudaEventDestroy(h->ev_out);
+    if (h->s_in) cudaStreamDestroy(h->s_in);
+    if (h->s_out) cudaStreamDestroy(h->s_out);
     if (h->d_status) cudaFree(h->d_status);
     if (h->stage) cudaFree(h->stage);
     delete h;
@@ -293,6 +307,14 @@ int f2k_attn_forward_fused(f2k_attn* h, const void* q_txt, const void* k_txt, co
     return F2K_OK;
 }
 
+// Host buffers in, host buffers out. The heads are independent, so the call is a pipeline over
+// head groups: while the copy engine brings in Q, K, V of group g+1 (2-D copies that pick the
+// group's columns out of the [batch, seq, heads, 128] host tensors), the SMs run the prologue and
+// the attention of group g on a contiguous [batch, seq, heads/groups, 128] staging copy, and the
+// other copy engine sends the output of group g-1 back. The host-to-device leg is the long one
+// (three inputs per output), so the step takes about its time plus the last group's kernels and
+// output copy. Stream order as seen by the caller is unchanged: the call starts after earlier work
+// on `stream`, and later work on `stream` starts after the last output copy.
 int f2k_attn_forward_fused_host(f2k_attn* h, const void* hq_txt, const void* hk_txt,
                                 const void* hv_txt, const void* hq_img, const void* hk_img,
                                 const void* hv_img, const void* gamma_q_txt,
@@ -302,48 +324,119 @@ int f2k_attn_forward_fused_host(f2k_attn* h, const void* hq_txt, const void* hk_
                                 float eps, void* ho_txt, void* ho_img, void* stream) {
     if (!h) return F2K_ERR_INVALID;
     if (!h->valid) return F2K_ERR_INVALID;
-    const bool has_txt = h->cfg.seq_txt > 0;
+    const f2k_attn_config& c = h->cfg;
+    const bool has_txt = c.seq_txt > 0;
     if (!hq_img || !hk_img || !hv_img || !ho_img ||
         (has_txt && (!hq_txt || !hk_txt || !hv_txt || !ho_txt)))
         return fail(h, F2K_ERR_INVALID, "null host pointer");
-    const size_t bt = align_up(h->bytes_txt(), kAlign), bi = align_up(h->bytes_img(), kAlign);
-    const size_t need = 4 * bt + 4 * bi + h->fused_ws();
+    cudaError_t e = cudaSuccess;
+    if (h->child.empty()) {
+        // first call: split into head groups (none for small problems, where the extra copies cost
+        // more than the overlap gains), make the children, streams and events
+        int groups = 1;
+        if (3 * h->bytes_img() >= ((size_t)4 << 20)) {
+            if (c.n_heads % 8 == 0 && c.n_heads >= 16) groups = 8;      // measured best for 32 heads
+            else if (c.n_heads % 4 == 0 && c.n_heads >= 8) groups = 4;
+            else if (c.n_heads % 2 == 0 && c.n_heads >= 4) groups = 2;
+        }
+        if (const char* env = std::getenv("F2K_HOST_GROUPS")) {          // measurement knob
+            const int g = std::atoi(env);
+            if (g >= 1 && c.n_heads % g == 0) groups = g;
+        }
+        f2k_attn_config cc = c;
+        cc.n_heads = c.n_heads / groups;
+        cc.scale   = h->scale;
+        for (int g = 0; g < groups; ++g) {
+            f2k_attn* ch = nullptr;
+            const int rc = f2k_attn_create(&cc, &ch);
+            if (ch) h->child.push_back(ch);
+            if (rc != F2K_OK) {
+                const std::string msg = std::string("head-group handle: ") + f2k_attn_last_error(ch);
+                for (f2k_attn* x : h->child) f2k_attn_destroy(x);
+                h->child.clear();
+                return fail(h, rc, msg);
+            }
+        }
+        h->arrived.assign(groups, nullptr);
+        h->computed.assign(groups, nullptr);
+        for (int g = 0; g < groups && e == cudaSuccess; ++g) {
+            e = cudaEventCreateWithFlags(&h->arrived[g], cudaEventDisableTiming);
+            if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->computed[g], cudaEventDisableTiming);
+        }
+        if (e == cudaSuccess && !h->ev_start) e = cudaEventCreateWithFlags(&h->ev_start, cudaEventDisableTiming);
+        if (e == cudaSuccess && !h->ev_out) e = cudaEventCreateWithFlags(&h->ev_out, cudaEventDisableTiming);
+        if (e == cudaSuccess && !h->s_in) e = cudaStreamCreateWithFlags(&h->s_in, cudaStreamNonBlocking);
+        if (e == cudaSuccess && !h->s_out) e = cudaStreamCreateWithFlags(&h->s_out, cudaStreamNonBlocking);
+        if (e != cudaSuccess) {
+            for (f2k_attn* x : h->child) f2k_attn_destroy(x);
+            h->child.clear();
+            return fail_cuda(h, "host pipeline set-up", e);
+        }
+    }
+    const int groups = (int)h->child.size();
+    f2k_attn* c0 = h->child[0];
+    const int nh = c0->cfg.n_heads;
+    const size_t bt = align_up(c0->bytes_txt(), kAlign), bi = align_up(c0->bytes_img(), kAlign);
+    const size_t per_group = 4 * bt + 4 * bi + c0->fused_ws();
+    const size_t need = per_group * groups;
     if (h->stage_bytes < need) {
         if (h->stage) cudaFree(h->stage);
         h->stage = nullptr;
         h->stage_bytes = 0;
-        const cudaError_t e = cudaMalloc(&h->stage, need);
+        e = cudaMalloc(&h->stage, need);
         if (e != cudaSuccess) return fail_cuda(h, "cudaMalloc(staging)", e);
         h->stage_bytes = need;
     }
-    uint8_t* d = static_cast<uint8_t*>(h->stage);
-    void* dq_t = d;            void* dk_t = d + bt;       void* dv_t = d + 2 * bt;  void* do_t = d + 3 * bt;
-    uint8_t* di = d + 4 * bt;
-    void* dq_i = di;           void* dk_i = di + bi;      void* dv_i = di + 2 * bi; void* do_i = di + 3 * bi;
-    void* ws = di + 4 * bi;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    cudaError_t e = cudaSuccess;
-    auto h2d = [&](void* dst, const void* src, size_t n) {
-        if (e == cudaSuccess && n) e = cudaMemcpyAsync(dst, src, n, cudaMemcpyHostToDevice, s);
+    const size_t hpitch = (size_t)c.n_heads * kHeadDim * 2;   // one token of all heads on the host
+    const size_t dpitch = (size_t)nh * kHeadDim * 2;          // one token of the group on the device
+    const size_t rows_t = (size_t)c.batch * c.seq_txt, rows_i = (size_t)c.batch * c.seq_img;
+    auto h2d = [&](void* dst, const void* src, size_t rows, int g) {
+        if (e == cudaSuccess && rows)
+            e = cudaMemcpy2DAsync(dst, dpitch, static_cast<const uint8_t*>(src) + g * dpitch, hpitch, dpitch, rows,
+                                  cudaMemcpyHostToDevice, h->s_in);
     };
-    if (has_txt) {
-        h2d(dq_t, hq_txt, h->bytes_txt());
-        h2d(dk_t, hk_txt, h->bytes_txt());
-        h2d(dv_t, hv_txt, h->bytes_txt());
+    auto d2h = [&](void* dst, const void* src, size_t rows, int g) {
+        if (e == cudaSuccess && rows)
+            e = cudaMemcpy2DAsync(static_cast<uint8_t*>(dst) + g * dpitch, hpitch, src, dpitch, dpitch, rows,
+                                  cudaMemcpyDeviceToHost, h->s_out);
+    };
+    e = cudaEventRecord(h->ev_start, s);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(h->s_in, h->ev_start, 0);
+    if (e != cudaSuccess) return fail_cuda(h, "event", e);
+    for (int g = 0; g < groups; ++g) {
+        uint8_t* d = static_cast<uint8_t*>(h->stage) + g * per_group;
+        void* dq_t = d;            void* dk_t = d + bt;       void* dv_t = d + 2 * bt;  void* do_t = d + 3 * bt;
+        uint8_t* di = d + 4 * bt;
+        void* dq_i = di;           void* dk_i = di + bi;      void* dv_i = di + 2 * bi; void* do_i = di + 3 * bi;
+        void* ws = di + 4 * bi;
+        if (has_txt) {
+            h2d(dq_t, hq_txt, rows_t, g);
+            h2d(dk_t, hk_txt, rows_t, g);
+            h2d(dv_t, hv_txt, rows_t, g);
+        }
+        h2d(dq_i, hq_img, rows_i, g);
+        h2d(dk_i, hk_img, rows_i, g);
+        h2d(dv_i, hv_img, rows_i, g);
+        if (e == cudaSuccess) e = cudaEventRecord(h->arrived[g], h->s_in);
+        if (e == cudaSuccess) e = cudaStreamWaitEvent(s, h->arrived[g], 0);
+        if (e != cudaSuccess) return fail_cuda(h, "host-to-device copy", e);
+        f2k_attn* ch = h->child[g];
+        const int rc = f2k_attn_forward_fused(ch, has_txt ? dq_t : nullptr, has_txt ? dk_t : nullptr,
+                                              has_txt ? dv_t : nullptr, dq_i, dk_i, dv_i, gamma_q_txt,
+                                              gamma_k_txt, gamma_q_img, gamma_k_img, cos_txt, sin_txt,
+                                              cos_img, sin_img, eps, has_txt ? do_t : nullptr, do_i, ws,
+                                              ch->fused_ws(), stream);
+        if (rc != F2K_OK) return fail(h, rc, ch->err);
+        e = cudaEventRecord(h->computed[g], s);
+        if (e == cudaSuccess) e = cudaStreamWaitEvent(h->s_out, h->computed[g], 0);
+        if (has_txt) d2h(ho_txt, do_t, rows_t, g);
+        d2h(ho_img, do_i, rows_i, g);
+        if (e != cudaSuccess) return fail_cuda(h, "device-to-host copy", e);
     }
-    h2d(dq_i, hq_img, h->bytes_img());
-    h2d(dk_i, hk_img, h->bytes_img());
-    h2d(dv_i, hv_img, h->bytes_img());
-    if (e != cudaSuccess) return fail_cuda(h, "host-to-device copy", e);
-    const int rc = f2k_attn_forward_fused(h, has_txt ? dq_t : nullptr, has_txt ? dk_t : nullptr,
-                                          has_txt ? dv_t : nullptr, dq_i, dk_i, dv_i, gamma_q_txt,
-                                          gamma_k_txt, gamma_q_img, gamma_k_img, cos_txt, sin_txt,
-                                          cos_img, sin_img, eps, has_txt ? do_t : nullptr, do_i, ws,
-                                          h->fused_ws(), stream);
-    if (rc != F2K_OK) return rc;
-    if (has_txt) e = cudaMemcpyAsync(ho_txt, do_t, h->bytes_txt(), cudaMemcpyDeviceToHost, s);
-    if (e == cudaSuccess) e = cudaMemcpyAsync(ho_img, do_i, h->bytes_img(), cudaMemcpyDeviceToHost, s);
-    if (e != cudaSuccess) return fail_cuda(h, "device-to-host copy", e);
+    e = cudaEventRecord(h->ev_out, h->s_out);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(s, h->ev_out, 0);
+    if (e != cudaSuccess) return fail_cuda(h, "event", e);
     return F2K_OK;
 }
 
@@ -357,6 +450,11 @@ int f2k_attn_device_status(f2k_attn* h, int* status_out) {
     if (st != 0) {
         e = cudaMemset(h->d_status, 0, sizeof st);
         if (e != cudaSuccess) return fail_cuda(h, "status clear", e);
+    }
+    for (f2k_attn* ch : h->child) {      // head-group handles of the host-buffer entry point
+        int cst = 0;
+        f2k_attn_device_status(ch, &cst);
+        st |= cst;
     }
     if (status_out) *status_out = st;
     if (st != 0) return fail(h, F2K_ERR_DEVICE, "a bounded wait inside the attention kernel expired");

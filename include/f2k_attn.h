@@ -104,8 +104,12 @@ int f2k_attn_forward_fused(f2k_attn* h,
 
 /* Same computation as f2k_attn_forward_fused with q, k, v, o in HOST memory (pinned
  * memory makes the copies asynchronous); gains and tables stay device pointers, like
- * the construction-time uploads of the reference. Copies in, computes and copies out
- * on `stream` without synchronising. Device staging is allocated on the first call.
+ * the construction-time uploads of the reference. Never synchronises: the call starts
+ * after earlier work on `stream`, and later work on `stream` starts after the outputs
+ * are in host memory. Inside, larger problems run as a pipeline over groups of heads on
+ * two transfer streams the handle owns, so that the copies in, the kernels and the
+ * copies out of different groups overlap. Device staging, streams and per-group state
+ * are allocated on the first call.
  * No counterpart in the reference, whose callers always hold device buffers; it exists
  * so that end-to-end time including host<->device traffic can be measured. */
 int f2k_attn_forward_fused_host(f2k_attn* h,

@@ -298,14 +298,15 @@ def test_4608_properties(f2k, big):
     assert_parity(q_i, base_i, "key permutation img", max_abs_tol=1e-2, cos_tol=0.99999)
 
 
-def test_host_buffer_entry_point(f2k, orc):
+@pytest.mark.parametrize("heads", [4, 8, 6])     # one group; four groups of two heads; two groups of three
+def test_host_buffer_entry_point(f2k, orc, heads):
     import torch
     from f2k_cuda_b200.inputs import WORKLOADS, make_problem
     w = WORKLOADS["s1152"]
-    p = make_problem(w, heads=4)
+    p = make_problem(w, heads=heads)
     tabs = (*f2k.build_rope_4axis_tables((32,) * 4, p.pos_txt, 2000.0),
             *f2k.build_rope_4axis_tables((32,) * 4, p.pos_img, 2000.0))
-    ja = f2k.JointAttention(f2k.JointAttention.Config(w.batch, w.seq_txt, w.seq_img, 4, 128))
+    ja = f2k.JointAttention(f2k.JointAttention.Config(w.batch, w.seq_txt, w.seq_img, heads, 128))
     assert ja.ok(), ja.last_error()
     pin = lambda b: torch.from_numpy(b.view(np.int16)).view(torch.bfloat16).pin_memory()  # noqa: E731
     hin = [pin(x) for x in (p.q_txt, p.k_txt, p.v_txt, p.q_img, p.k_img, p.v_img)]
