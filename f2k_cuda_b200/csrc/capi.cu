@@ -7,6 +7,7 @@
 
 #include "attn_launch.h"
 
+#include <algorithm>
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
@@ -94,6 +95,8 @@ struct f2k_attn {
     void*  stage = nullptr;
     size_t stage_bytes = 0;
     std::vector<f2k_attn*>   child;
+    std::vector<AttnParams>  chunk_params;   // batch 1: one launch per chunk of query rows
+    cudaEvent_t  ev_k = nullptr, ev_v = nullptr;
     std::vector<cudaEvent_t> arrived, computed;
     cudaStream_t s_in = nullptr, s_out = nullptr;
     cudaEvent_t  ev_start = nullptr, ev_out = nullptr;
@@ -117,6 +120,56 @@ int fail_cuda(f2k_attn* h, const char* what, cudaError_t e) {
     return fail(h, F2K_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
 }
 
+struct QSeg  { const void* q; void* o; int len; };
+struct KvSeg { const void* k; const void* v; int len; };
+
+// Launch parameters for attention of the given query segments over the given key/value segments;
+// every segment is bf16 [batch, len, heads, 128], dense.
+int build_params(f2k_attn* h, AttnParams& p, const QSeg* qs, int nq, const KvSeg* kvs, int nkv) {
+    const f2k_attn_config& c = h->cfg;
+    std::memset(&p, 0, sizeof p);
+    const long long tok = (long long)c.n_heads * kHeadDim;
+    if (nq < 1 || nq > kMaxQSeg || nkv < 1 || nkv > kMaxKvSeg) return fail(h, F2K_ERR_INVALID, "segment count");
+    int tiles = 0;
+    for (int s = 0; s < nq; ++s) {
+        const QSeg& g = qs[s];
+        if (!g.q || !g.o) return fail(h, F2K_ERR_INVALID, "null tensor pointer");
+        if ((reinterpret_cast<uintptr_t>(g.o) & 15u) != 0)
+            return fail(h, F2K_ERR_INVALID, "output pointer is not 16-byte aligned");
+        const long long bstride = (long long)g.len * tok;
+        if (!encode_segment(&p.tm_q[s], g.q, g.len, c.n_heads, c.batch, tok, bstride, h->err)) return F2K_ERR_CUDA;
+        p.o_ptr[s]          = g.o;
+        p.o_tok_stride[s]   = tok;
+        p.o_batch_stride[s] = bstride;
+        p.q_len[s]          = g.len;
+        p.q_tile_start[s]   = tiles;
+        tiles += (g.len + kTileM - 1) / kTileM;
+    }
+    p.q_tile_start[nq] = tiles;
+    p.n_qseg    = nq;
+    p.n_q_tiles = tiles;
+    tiles = 0;
+    for (int s = 0; s < nkv; ++s) {
+        const KvSeg& g = kvs[s];
+        if (!g.k || !g.v) return fail(h, F2K_ERR_INVALID, "null tensor pointer");
+        const long long bstride = (long long)g.len * tok;
+        if (!encode_segment(&p.tm_k[s], g.k, g.len, c.n_heads, c.batch, tok, bstride, h->err) ||
+            !encode_segment(&p.tm_v[s], g.v, g.len, c.n_heads, c.batch, tok, bstride, h->err))
+            return F2K_ERR_CUDA;
+        p.kv_len[s]        = g.len;
+        p.kv_tile_start[s] = tiles;
+        tiles += (g.len + kTileN - 1) / kTileN;
+    }
+    p.kv_tile_start[nkv] = tiles;
+    p.n_kvseg    = nkv;
+    p.n_kv_tiles = tiles;
+    p.n_heads    = c.n_heads;
+    p.batch      = c.batch;
+    p.scale_log2 = h->scale * 1.4426950408889634f;
+    p.status     = h->d_status;
+    return F2K_OK;
+}
+
 // Builds (or reuses) the launch parameters for attention over the text||image
 // segments held at the given pointers.
 int prepare_params(f2k_attn* h, const void* q_txt, const void* k_txt, const void* v_txt,
@@ -128,47 +181,164 @@ int prepare_params(f2k_attn* h, const void* q_txt, const void* k_txt, const void
         std::memcmp(out, h->last_out, sizeof out) == 0)
         return F2K_OK;
     h->have_params = false;
-
     const f2k_attn_config& c = h->cfg;
-    AttnParams& p = h->params;
-    std::memset(&p, 0, sizeof p);
-    const long long tok = (long long)c.n_heads * kHeadDim;
-
-    struct Seg { const void *q, *k, *v; void* o; int len; };
-    Seg segs[2];
+    QSeg  qs[2];
+    KvSeg kvs[2];
     int n = 0;
-    if (c.seq_txt > 0) segs[n++] = {q_txt, k_txt, v_txt, o_txt, c.seq_txt};
-    segs[n++] = {q_img, k_img, v_img, o_img, c.seq_img};
-
-    int tiles = 0;
-    for (int s = 0; s < n; ++s) {
-        const Seg& g = segs[s];
-        if (!g.q || !g.k || !g.v || !g.o) return fail(h, F2K_ERR_INVALID, "null tensor pointer");
-        if ((reinterpret_cast<uintptr_t>(g.o) & 15u) != 0)
-            return fail(h, F2K_ERR_INVALID, "output pointer is not 16-byte aligned");
-        const long long bstride = (long long)g.len * tok;
-        if (!encode_segment(&p.tm_q[s], g.q, g.len, c.n_heads, c.batch, tok, bstride, h->err) ||
-            !encode_segment(&p.tm_k[s], g.k, g.len, c.n_heads, c.batch, tok, bstride, h->err) ||
-            !encode_segment(&p.tm_v[s], g.v, g.len, c.n_heads, c.batch, tok, bstride, h->err))
-            return F2K_ERR_CUDA;
-        p.o_ptr[s]          = g.o;
-        p.o_tok_stride[s]   = tok;
-        p.o_batch_stride[s] = bstride;
-        p.q_len[s] = p.kv_len[s] = g.len;
-        p.q_tile_start[s] = p.kv_tile_start[s] = tiles;
-        tiles += (g.len + kTileM - 1) / kTileM;
+    if (c.seq_txt > 0) {
+        qs[n]  = {q_txt, o_txt, c.seq_txt};
+        kvs[n] = {k_txt, v_txt, c.seq_txt};
+        ++n;
     }
-    p.q_tile_start[n] = p.kv_tile_start[n] = tiles;
-    p.n_qseg = p.n_kvseg = n;
-    p.n_q_tiles = p.n_kv_tiles = tiles;
-    p.n_heads    = c.n_heads;
-    p.batch      = c.batch;
-    p.scale_log2 = h->scale * 1.4426950408889634f;
-    p.status     = h->d_status;
-
+    qs[n]  = {q_img, o_img, c.seq_img};
+    kvs[n] = {k_img, v_img, c.seq_img};
+    ++n;
+    for (int i = 0; i < n; ++i)
+        if (!qs[i].q || !kvs[i].k || !kvs[i].v || !qs[i].o) return fail(h, F2K_ERR_INVALID, "null tensor pointer");
+    const int rc = build_params(h, h->params, qs, n, kvs, n);
+    if (rc != F2K_OK) return rc;
     std::memcpy(h->last_in, in, sizeof in);
     std::memcpy(h->last_out, out, sizeof out);
     h->have_params = true;
+    return F2K_OK;
+}
+
+// ---- host-buffer entry point: set-up shared by its two pipelines ----
+cudaError_t ensure_pipe(f2k_attn* h, int n_stages) {
+    cudaError_t e = cudaSuccess;
+    while ((int)h->arrived.size() < n_stages && e == cudaSuccess) {
+        cudaEvent_t a = nullptr, b = nullptr;
+        e = cudaEventCreateWithFlags(&a, cudaEventDisableTiming);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&b, cudaEventDisableTiming);
+        if (e == cudaSuccess) { h->arrived.push_back(a); h->computed.push_back(b); }
+    }
+    for (cudaEvent_t* ev : {&h->ev_start, &h->ev_out, &h->ev_k, &h->ev_v})
+        if (e == cudaSuccess && !*ev) e = cudaEventCreateWithFlags(ev, cudaEventDisableTiming);
+    if (e == cudaSuccess && !h->s_in) e = cudaStreamCreateWithFlags(&h->s_in, cudaStreamNonBlocking);
+    if (e == cudaSuccess && !h->s_out) e = cudaStreamCreateWithFlags(&h->s_out, cudaStreamNonBlocking);
+    return e;
+}
+
+constexpr int kChunkRows = 1024;   // query rows per launch of the batch-1 pipeline: 4 CTA pairs per head
+
+// Batch 1: every transfer is one linear copy. K and V go in first, whole; then the query rows in
+// chunks of kChunkRows of the joint (text, then image) sequence. A chunk's rows are normalised,
+// attended over all keys and sent back while the next chunk's rows are still coming in, so the step
+// takes the host-to-device time of Q, K, V plus the last chunk's kernels and output copy.
+int host_row_chunks(f2k_attn* h, const void* hq_txt, const void* hk_txt, const void* hv_txt,
+                    const void* hq_img, const void* hk_img, const void* hv_img, const void* gamma_q_txt,
+                    const void* gamma_k_txt, const void* gamma_q_img, const void* gamma_k_img,
+                    const float* cos_txt, const float* sin_txt, const float* cos_img, const float* sin_img,
+                    float eps, void* ho_txt, void* ho_img, cudaStream_t s) {
+    const f2k_attn_config& c = h->cfg;
+    const int St = c.seq_txt, Si = c.seq_img, S = St + Si;
+    const int n_chunks = (S + kChunkRows - 1) / kChunkRows;
+    cudaError_t e = ensure_pipe(h, n_chunks);
+    if (e != cudaSuccess) return fail_cuda(h, "host pipeline set-up", e);
+    const size_t bt = align_up(h->bytes_txt(), kAlign), bi = align_up(h->bytes_img(), kAlign);
+    const size_t need = 4 * bt + 4 * bi + h->fused_ws();
+    if (h->stage_bytes < need) {
+        if (h->stage) cudaFree(h->stage);
+        h->stage = nullptr;
+        h->stage_bytes = 0;
+        h->chunk_params.clear();
+        e = cudaMalloc(&h->stage, need);
+        if (e != cudaSuccess) return fail_cuda(h, "cudaMalloc(staging)", e);
+        h->stage_bytes = need;
+    }
+    uint8_t* d = static_cast<uint8_t*>(h->stage);
+    uint8_t *dq_t = d, *dk_t = d + bt, *dv_t = d + 2 * bt, *do_t = d + 3 * bt;
+    uint8_t* di = d + 4 * bt;
+    uint8_t *dq_i = di, *dk_i = di + bi, *dv_i = di + 2 * bi, *do_i = di + 3 * bi;
+    uint8_t* ws = di + 4 * bi;
+    uint8_t *qn_t = ws, *kn_t = ws + bt, *qn_i = ws + 2 * bt, *kn_i = ws + 2 * bt + bi;
+    const size_t tokb = (size_t)c.n_heads * kHeadDim * 2;       // bytes of one token, all heads
+
+    // the rows of chunk i: [t0, t1) of the text stream and [i0, i1) of the image stream
+    auto chunk_rows = [&](int i, int& t0, int& t1, int& i0, int& i1) {
+        const int r0 = i * kChunkRows, r1 = std::min(S, r0 + kChunkRows);
+        t0 = std::min(r0, St); t1 = std::min(r1, St);
+        i0 = std::max(r0, St) - St; i1 = std::max(r1, St) - St;
+    };
+    if ((int)h->chunk_params.size() != n_chunks) {
+        h->chunk_params.assign(n_chunks, AttnParams{});
+        KvSeg kvs[2];
+        int nkv = 0;
+        if (St > 0) kvs[nkv++] = {kn_t, dv_t, St};
+        kvs[nkv++] = {kn_i, dv_i, Si};
+        for (int i = 0; i < n_chunks; ++i) {
+            int t0, t1, i0, i1;
+            chunk_rows(i, t0, t1, i0, i1);
+            QSeg qs[2];
+            int nq = 0;
+            if (t1 > t0) qs[nq++] = {qn_t + t0 * tokb, do_t + t0 * tokb, t1 - t0};
+            if (i1 > i0) qs[nq++] = {qn_i + i0 * tokb, do_i + i0 * tokb, i1 - i0};
+            const int rc = build_params(h, h->chunk_params[i], qs, nq, kvs, nkv);
+            if (rc != F2K_OK) { h->chunk_params.clear(); return rc; }
+        }
+    }
+
+    auto copy = [&](void* dst, const void* src, size_t n, cudaMemcpyKind kind, cudaStream_t st) {
+        if (e == cudaSuccess && n) e = cudaMemcpyAsync(dst, src, n, kind, st);
+    };
+    QkPrologueParams pp;
+    long long rows = 0;
+    auto reset_jobs = [&]() { std::memset(&pp, 0, sizeof pp); rows = 0; pp.n_heads = c.n_heads; pp.eps = eps; };
+    auto add_job = [&](const void* x, void* y, const void* g, const float* ct, const float* sn, int len) {
+        QkPrologueJob& j = pp.job[pp.n_jobs];
+        j.x = x; j.y = y; j.gamma = g; j.cos_tab = ct; j.sin_tab = sn; j.seq = len;
+        j.rows = (long long)len * c.n_heads;
+        pp.row_start[pp.n_jobs] = rows;
+        rows += j.rows;
+        pp.row_start[++pp.n_jobs] = rows;
+    };
+
+    e = cudaEventRecord(h->ev_start, s);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(h->s_in, h->ev_start, 0);
+    copy(dk_t, hk_txt, h->bytes_txt(), cudaMemcpyHostToDevice, h->s_in);
+    copy(dk_i, hk_img, h->bytes_img(), cudaMemcpyHostToDevice, h->s_in);
+    if (e == cudaSuccess) e = cudaEventRecord(h->ev_k, h->s_in);
+    copy(dv_t, hv_txt, h->bytes_txt(), cudaMemcpyHostToDevice, h->s_in);
+    copy(dv_i, hv_img, h->bytes_img(), cudaMemcpyHostToDevice, h->s_in);
+    if (e == cudaSuccess) e = cudaEventRecord(h->ev_v, h->s_in);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(s, h->ev_k, 0);
+    if (e != cudaSuccess) return fail_cuda(h, "host-to-device copy (K, V)", e);
+    reset_jobs();
+    if (St > 0) add_job(dk_t, kn_t, gamma_k_txt, cos_txt, sin_txt, St);
+    add_job(dk_i, kn_i, gamma_k_img, cos_img, sin_img, Si);
+    e = qk_prologue_launch(pp, s);
+    if (e != cudaSuccess) return fail_cuda(h, "prologue launch (K)", e);
+
+    for (int i = 0; i < n_chunks; ++i) {
+        int t0, t1, i0, i1;
+        chunk_rows(i, t0, t1, i0, i1);
+        if (t1 > t0) copy(dq_t + t0 * tokb, static_cast<const uint8_t*>(hq_txt) + t0 * tokb, (t1 - t0) * tokb,
+                          cudaMemcpyHostToDevice, h->s_in);
+        if (i1 > i0) copy(dq_i + i0 * tokb, static_cast<const uint8_t*>(hq_img) + i0 * tokb, (i1 - i0) * tokb,
+                          cudaMemcpyHostToDevice, h->s_in);
+        if (e == cudaSuccess) e = cudaEventRecord(h->arrived[i], h->s_in);
+        if (e == cudaSuccess) e = cudaStreamWaitEvent(s, h->arrived[i], 0);
+        if (e == cudaSuccess && i == 0) e = cudaStreamWaitEvent(s, h->ev_v, 0);
+        if (e != cudaSuccess) return fail_cuda(h, "host-to-device copy (Q)", e);
+        reset_jobs();
+        if (t1 > t0) add_job(dq_t + t0 * tokb, qn_t + t0 * tokb, gamma_q_txt, cos_txt + (size_t)t0 * 64,
+                             sin_txt + (size_t)t0 * 64, t1 - t0);
+        if (i1 > i0) add_job(dq_i + i0 * tokb, qn_i + i0 * tokb, gamma_q_img, cos_img + (size_t)i0 * 64,
+                             sin_img + (size_t)i0 * 64, i1 - i0);
+        e = qk_prologue_launch(pp, s);
+        if (e == cudaSuccess) e = attn_fwd_launch(h->chunk_params[i], s);
+        if (e != cudaSuccess) return fail_cuda(h, "kernel launch", e);
+        e = cudaEventRecord(h->computed[i], s);
+        if (e == cudaSuccess) e = cudaStreamWaitEvent(h->s_out, h->computed[i], 0);
+        if (t1 > t0) copy(static_cast<uint8_t*>(ho_txt) + t0 * tokb, do_t + t0 * tokb, (t1 - t0) * tokb,
+                          cudaMemcpyDeviceToHost, h->s_out);
+        if (i1 > i0) copy(static_cast<uint8_t*>(ho_img) + i0 * tokb, do_i + i0 * tokb, (i1 - i0) * tokb,
+                          cudaMemcpyDeviceToHost, h->s_out);
+        if (e != cudaSuccess) return fail_cuda(h, "device-to-host copy", e);
+    }
+    e = cudaEventRecord(h->ev_out, h->s_out);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(s, h->ev_out, 0);
+    if (e != cudaSuccess) return fail_cuda(h, "event", e);
     return F2K_OK;
 }
 
@@ -219,6 +389,8 @@ void f2k_attn_destroy(f2k_attn* h) {
     for (cudaEvent_t e : h->arrived) cudaEventDestroy(e);
     for (cudaEvent_t e : h->computed) cudaEventDestroy(e);
     if (h->ev_start) cudaEventDestroy(h->ev_start);
+    if (h->ev_k) cudaEventDestroy(h->ev_k);
+    if (h->ev_v) cudaEventDestroy(h->ev_v);
     if (h->ev_out) cudaEventDestroy(h->ev_out);
     if (h->s_in) cudaStreamDestroy(h->s_in);
     if (h->s_out) cudaStreamDestroy(h->s_out);
@@ -307,8 +479,9 @@ int f2k_attn_forward_fused(f2k_attn* h, const void* q_txt, const void* k_txt, co
     return F2K_OK;
 }
 
-// Host buffers in, host buffers out. The heads are independent, so the call is a pipeline over
-// head groups: while the copy engine brings in Q, K, V of group g+1 (2-D copies that pick the
+// Host buffers in, host buffers out, as a pipeline on two transfer streams of the handle and the
+// caller's stream. Batch 1 splits the query rows (host_row_chunks above). Larger batches split the
+// heads, which are independent: while the copy engine brings in Q, K, V of group g+1 (2-D copies that pick the
 // group's columns out of the [batch, seq, heads, 128] host tensors), the SMs run the prologue and
 // the attention of group g on a contiguous [batch, seq, heads/groups, 128] staging copy, and the
 // other copy engine sends the output of group g-1 back. The host-to-device leg is the long one
@@ -329,12 +502,22 @@ int f2k_attn_forward_fused_host(f2k_attn* h, const void* hq_txt, const void* hk_
     if (!hq_img || !hk_img || !hv_img || !ho_img ||
         (has_txt && (!hq_txt || !hk_txt || !hv_txt || !ho_txt)))
         return fail(h, F2K_ERR_INVALID, "null host pointer");
+    const bool big = 3 * h->bytes_img() >= ((size_t)4 << 20);    // small problems: one pass
+    const char* mode = std::getenv("F2K_HOST_PIPELINE");         // measurement knob: "heads" or "rows"
+    const bool want_rows = mode ? std::strcmp(mode, "rows") == 0 : (c.batch == 1 && big);
+    if (!gamma_q_img || !gamma_k_img || !cos_img || !sin_img ||
+        (has_txt && (!gamma_q_txt || !gamma_k_txt || !cos_txt || !sin_txt)))
+        return fail(h, F2K_ERR_INVALID, "null tensor pointer");
+    if (want_rows && c.batch == 1)
+        return host_row_chunks(h, hq_txt, hk_txt, hv_txt, hq_img, hk_img, hv_img, gamma_q_txt, gamma_k_txt,
+                               gamma_q_img, gamma_k_img, cos_txt, sin_txt, cos_img, sin_img, eps, ho_txt, ho_img,
+                               static_cast<cudaStream_t>(stream));
     cudaError_t e = cudaSuccess;
     if (h->child.empty()) {
         // first call: split into head groups (none for small problems, where the extra copies cost
         // more than the overlap gains), make the children, streams and events
         int groups = 1;
-        if (3 * h->bytes_img() >= ((size_t)4 << 20)) {
+        if (big) {
             if (c.n_heads % 8 == 0 && c.n_heads >= 16) groups = 8;      // measured best for 32 heads
             else if (c.n_heads % 4 == 0 && c.n_heads >= 8) groups = 4;
             else if (c.n_heads % 2 == 0 && c.n_heads >= 4) groups = 2;
@@ -357,16 +540,7 @@ int f2k_attn_forward_fused_host(f2k_attn* h, const void* hq_txt, const void* hk_
                 return fail(h, rc, msg);
             }
         }
-        h->arrived.assign(groups, nullptr);
-        h->computed.assign(groups, nullptr);
-        for (int g = 0; g < groups && e == cudaSuccess; ++g) {
-            e = cudaEventCreateWithFlags(&h->arrived[g], cudaEventDisableTiming);
-            if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->computed[g], cudaEventDisableTiming);
-        }
-        if (e == cudaSuccess && !h->ev_start) e = cudaEventCreateWithFlags(&h->ev_start, cudaEventDisableTiming);
-        if (e == cudaSuccess && !h->ev_out) e = cudaEventCreateWithFlags(&h->ev_out, cudaEventDisableTiming);
-        if (e == cudaSuccess && !h->s_in) e = cudaStreamCreateWithFlags(&h->s_in, cudaStreamNonBlocking);
-        if (e == cudaSuccess && !h->s_out) e = cudaStreamCreateWithFlags(&h->s_out, cudaStreamNonBlocking);
+        e = ensure_pipe(h, groups);
         if (e != cudaSuccess) {
             for (f2k_attn* x : h->child) f2k_attn_destroy(x);
             h->child.clear();
@@ -383,6 +557,7 @@ int f2k_attn_forward_fused_host(f2k_attn* h, const void* hq_txt, const void* hk_
         if (h->stage) cudaFree(h->stage);
         h->stage = nullptr;
         h->stage_bytes = 0;
+        h->chunk_params.clear();
         e = cudaMalloc(&h->stage, need);
         if (e != cudaSuccess) return fail_cuda(h, "cudaMalloc(staging)", e);
         h->stage_bytes = need;

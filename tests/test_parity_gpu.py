@@ -298,11 +298,18 @@ def test_4608_properties(f2k, big):
     assert_parity(q_i, base_i, "key permutation img", max_abs_tol=1e-2, cos_tol=0.99999)
 
 
-@pytest.mark.parametrize("heads", [4, 8, 6])     # one group; four groups of two heads; two groups of three
-def test_host_buffer_entry_point(f2k, orc, heads):
+# (batch, heads, pipeline): None = the library's choice. Batch 1 and large enough: chunks of query
+# rows; "heads": groups of heads (4 groups of 2, 2 groups of 3); small problems: one pass.
+@pytest.mark.parametrize("batch,heads,mode", [(1, 4, None), (1, 8, None), (1, 4, "rows"), (1, 8, "heads"),
+                                              (1, 6, "heads"), (2, 8, None)])
+def test_host_buffer_entry_point(f2k, orc, monkeypatch, batch, heads, mode):
     import torch
-    from f2k_cuda_b200.inputs import WORKLOADS, make_problem
-    w = WORKLOADS["s1152"]
+    from f2k_cuda_b200.inputs import Workload, make_problem
+    if mode:
+        monkeypatch.setenv("F2K_HOST_PIPELINE", mode)
+    else:
+        monkeypatch.delenv("F2K_HOST_PIPELINE", raising=False)
+    w = Workload("host", batch, 128, ((32, 32),), seed=0x4057)
     p = make_problem(w, heads=heads)
     tabs = (*f2k.build_rope_4axis_tables((32,) * 4, p.pos_txt, 2000.0),
             *f2k.build_rope_4axis_tables((32,) * 4, p.pos_img, 2000.0))
@@ -314,6 +321,7 @@ def test_host_buffer_entry_point(f2k, orc, heads):
     dg = [dev_bf16(g) for g in p.gammas]
     dtab = [torch.from_numpy(x).cuda() for x in tabs]
     for _ in range(2):       # second call reuses the staging buffers
+        ho_t.fill_(float("nan")); ho_i.fill_(float("nan"))
         assert ja.forward_fused_host(*hin, dg, dtab, 1e-6, ho_t, ho_i), ja.last_error()
         torch.cuda.synchronize()
     assert ja.device_status() == 0
