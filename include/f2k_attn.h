@@ -179,7 +179,11 @@ int f2k_build_rope_4axis_tables(const int* axes_dim, int n_axes,
  * over NVLink while the attention kernel already works on the shards that have arrived.
  * Call order per step: write this rank's normalised K and its V (on the compute stream) to the
  * pointers given by f2k_seqpar_local_kv, then f2k_seqpar_forward. No collective is needed: the
- * ranks announce "written" to each other through words in their shard buffers. */
+ * ranks announce "written" to each other through words in their shard buffers.
+ * Meant for one process per GPU. Several ranks on ONE GPU (an emulation for tests) work only if
+ * every rank's K/V is in place before the first rank calls forward (a rank's kernel fills the
+ * GPU and must never wait for another rank's kernels) and the process has at least two hardware
+ * queues per rank (CUDA_DEVICE_MAX_CONNECTIONS), so that no two streams share one. */
 typedef struct f2k_seqpar f2k_seqpar; /* opaque */
 
 typedef struct f2k_seqpar_config {
