@@ -63,6 +63,7 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the timed CPU leg")
     ap.add_argument("--no-reference-kernel", action="store_true",
                     help="skip the short leg that times the reference's rebuilt kernels beside ours (N = 1)")
+    ap.add_argument("--skip-denoise-step", action="store_true", help="skip the 32-call CUDA-graph leg (N = 1)")
     ap.add_argument("--skip-e2e", action="store_true",
                     help="skip the host-buffer leg (for short profiler captures; the line then has e2e null)")
     return ap.parse_args()
@@ -193,6 +194,48 @@ def cpu_baseline(problem, tabs, flops_per_head):
             "sample": f"batch element 0, heads 0..{n - 1} of {H} (S=4608): QK-norm + RoPE + fp32 attention, {t:.1f} s"}
 
 
+def denoise_step_leg(f2k, d, dg, dtab, o_t, o_i, ws, ja, B, St, Si, H, D, stream, flops_per_call):
+    """The 32 attention calls of one denoise step (reference: 8 DoubleStreamBlock + 24
+    SingleStreamBlock forwards), captured once as a CUDA graph and replayed: time per step and per
+    call without per-call launch overhead. Single-stream blocks see one combined stream."""
+    S = St + Si
+    single = f2k.Attention(f2k.Attention.Config(B, S, H, D))
+    if not single.ok():
+        return {"unavailable": single.last_error()}
+    qc, kc, vc = (torch.cat([d[i], d[i + 3]], 1).contiguous() for i in range(3))
+    oc = torch.empty_like(qc)
+    tab_c = [torch.cat([dtab[0], dtab[2]]).contiguous(), torch.cat([dtab[1], dtab[3]]).contiguous()]
+    ws_c = torch.empty(single.fused_workspace_size_bytes(), dtype=torch.uint8, device="cuda")
+    g_single = [None, None, dg[2], dg[3]]
+    t_single = [None, None, tab_c[0], tab_c[1]]
+
+    def one_step():
+        for _ in range(8):
+            if not ja.forward_fused(*d, dg, dtab, 1e-6, o_t, o_i, ws):
+                raise RuntimeError(ja.last_error())
+        for _ in range(24):
+            if not single.forward_fused(None, None, None, qc, kc, vc, g_single, t_single, 1e-6, None, oc, ws_c):
+                raise RuntimeError(single.last_error())
+
+    one_step()                                     # tensor maps built, kernels loaded
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            one_step()
+    torch.cuda.synchronize()
+    for _ in range(2):
+        graph.replay()
+    reps = 5
+    ms = time_region(graph.replay, reps, stream)
+    if ja.device_status() != 0 or single.device_status() != 0:
+        raise RuntimeError("attention kernel reported a device-side error in the denoise-step leg")
+    return {"calls": 32, "ms_per_step": ms, "ms_per_call": ms / 32, "value": 32 * flops_per_call / (ms * 1e-3) / 1e12,
+            "unit": UNIT, "launch": "one CUDA graph of 64 kernels, replayed", "steps": reps,
+            "what": "8 joint calls (512 + 4096 tokens) + 24 single-stream calls (4608 tokens), fused prologue each"}
+
+
 def run_ours(args, rank, world):
     import f2k_cuda_b200 as f2k
     dev = torch.cuda.current_device()
@@ -246,6 +289,12 @@ def run_ours(args, rank, world):
     for _ in range(3):
         attn_only()
     ms_attn = time_region(attn_only, args.steps, stream)
+
+    # ---- one denoise step of the transformer: 8 double-stream calls (text and image streams
+    # separate) + 24 single-stream calls (one combined 4608-token stream), as one CUDA graph
+    denoise = None
+    if world == 1 and not args.skip_denoise_step:
+        denoise = denoise_step_leg(f2k, d, dg, dtab, o_t, o_i, ws, ja, B, St, Si, H, D, stream, flops)
 
     # ---- end to end through host buffers
     ms_e2e, e2e_steps = None, 0
@@ -301,6 +350,8 @@ def run_ours(args, rank, world):
         "gpu_launches": 2 * args.steps,
         "clocks": clocks,
     }
+    if denoise is not None:
+        line["denoise_step"] = denoise
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(p, tabs, flops / H)
     if world == 1 and not args.no_reference_kernel:

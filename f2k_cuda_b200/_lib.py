@@ -25,6 +25,11 @@ class AttnConfig(C.Structure):
                 ("n_heads", C.c_int), ("head_dim", C.c_int), ("scale", C.c_float)]
 
 
+class AttnStrides(C.Structure):
+    """struct f2k_attn_strides: token strides in elements, 0 = dense"""
+    _fields_ = [(n, C.c_longlong) for n in ("q_txt", "k_txt", "v_txt", "o_txt", "q_img", "k_img", "v_img", "o_img")]
+
+
 def _declare(lib: C.CDLL) -> None:
     vp, i, f, sz = C.c_void_p, C.c_int, C.c_float, C.c_size_t
     lib.f2k_attn_create.restype = i
@@ -41,6 +46,8 @@ def _declare(lib: C.CDLL) -> None:
     lib.f2k_attn_forward.argtypes = [vp] * 10 + [sz, vp]
     lib.f2k_attn_forward_fused.restype = i
     lib.f2k_attn_forward_fused.argtypes = [vp] * 15 + [f, vp, vp, vp, sz, vp]
+    lib.f2k_attn_forward_fused_strided.restype = i
+    lib.f2k_attn_forward_fused_strided.argtypes = [vp] * 15 + [f, vp, vp, C.POINTER(AttnStrides), vp, sz, vp]
     lib.f2k_attn_forward_fused_host.restype = i
     lib.f2k_attn_forward_fused_host.argtypes = [vp] * 15 + [f, vp, vp, vp]
     lib.f2k_attn_forward_fused_noalloc.restype = i

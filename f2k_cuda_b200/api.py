@@ -63,6 +63,61 @@ class _Module:
         lib.f2k_attn_device_status(self._h, C.byref(st))
         return st.value
 
+    # ---- fused calls (no counterpart in the reference classes); a module without a text stream
+    # ---- passes None for every *_txt argument
+    def fused_workspace_size_bytes(self) -> int:
+        return int(lib.f2k_attn_fused_workspace_bytes(self._h)) if self.ok() else 0
+
+    def forward_fused(self, Q_txt, K_txt, V_txt, Q_img, K_img, V_img, gammas, tables, eps,
+                      O_txt, O_img, workspace, stream=None) -> bool:
+        """Raw projections in; per-head RMSNorm + RoPE + attention in one call.
+        gammas = (gq_txt, gk_txt, gq_img, gk_img) bf16 [128];
+        tables = (cos_txt, sin_txt, cos_img, sin_img) fp32 [seq, 64]."""
+        if not self.ok():
+            return False
+        _check_bf16(Q_txt, K_txt, V_txt, Q_img, K_img, V_img, O_txt, O_img, *gammas)
+        ws_bytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
+        return lib.f2k_attn_forward_fused(
+            self._h, _p(Q_txt), _p(K_txt), _p(V_txt), _p(Q_img), _p(K_img), _p(V_img),
+            *[_p(g) for g in gammas], *[_p(t) for t in tables], eps, _p(O_txt), _p(O_img),
+            _p(workspace), ws_bytes, _stream(stream)) == _lib.F2K_OK
+
+    def forward_fused_strided(self, Q_txt, K_txt, V_txt, Q_img, K_img, V_img, gammas, tables, eps,
+                              O_txt, O_img, workspace, stream=None) -> bool:
+        """forward_fused on views: every tensor is a [batch, seq, n_heads, 128] view whose token
+        rows may be slices of wider rows (e.g. columns of a fused projection output viewed with
+        as_strided); rows of all batch elements must be consecutive. The strides are read off the
+        views."""
+        if not self.ok():
+            return False
+        st = _lib.AttnStrides()
+        for name, t in (("q_txt", Q_txt), ("k_txt", K_txt), ("v_txt", V_txt), ("o_txt", O_txt),
+                        ("q_img", Q_img), ("k_img", K_img), ("v_img", V_img), ("o_img", O_img)):
+            if t is None:
+                continue
+            if t.dtype != torch.bfloat16 or t.dim() != 4 or t.stride(3) != 1 or t.stride(2) != t.shape[3] \
+                    or (t.shape[0] > 1 and t.stride(0) != t.shape[1] * t.stride(1)):
+                raise TypeError("tensors must be bfloat16 [batch, seq, heads, 128] views with dense heads and "
+                                "consecutive token rows")
+            setattr(st, name, t.stride(1))
+        _check_bf16(*gammas)
+        ws_bytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
+        return lib.f2k_attn_forward_fused_strided(
+            self._h, _p(Q_txt), _p(K_txt), _p(V_txt), _p(Q_img), _p(K_img), _p(V_img),
+            *[_p(g) for g in gammas], *[_p(t) for t in tables], eps, _p(O_txt), _p(O_img),
+            C.byref(st), _p(workspace), ws_bytes, _stream(stream)) == _lib.F2K_OK
+
+    def forward_fused_host(self, hQ_txt, hK_txt, hV_txt, hQ_img, hK_img, hV_img, gammas, tables,
+                           eps, hO_txt, hO_img, stream=None) -> bool:
+        """Same as forward_fused with q, k, v, o in (pinned) host memory; gammas and tables on
+        the GPU. Asynchronous on the stream."""
+        if not self.ok():
+            return False
+        return lib.f2k_attn_forward_fused_host(
+            self._h, _p(hQ_txt), _p(hK_txt), _p(hV_txt), _p(hQ_img), _p(hK_img), _p(hV_img),
+            *[_p(g) for g in gammas], *[_p(t) for t in tables], eps, _p(hO_txt), _p(hO_img),
+            _stream(stream)) == _lib.F2K_OK
+
 
 class Attention(_Module):
     """Mirror of f2k::cuda::Attention: softmax(scale * Q K^T) V per head, non-causal."""
@@ -85,6 +140,15 @@ class Attention(_Module):
         return lib.f2k_attn_forward(self._h, None, None, None, _p(Q), _p(K), _p(V), None, _p(O),
                                     None, 0, _stream(stream)) == _lib.F2K_OK
 
+    def forward_fused_single(self, Q, K, V, gamma_q, gamma_k, cos, sin, eps, O, workspace, stream=None,
+                             strided: bool = False) -> bool:
+        """Raw projections of one combined stream in (the single-stream block's call):
+        per-head RMSNorm + RoPE + attention. strided=True takes [batch, seq, heads, 128] views
+        whose token rows are slices of wider rows."""
+        call = self.forward_fused_strided if strided else self.forward_fused
+        return call(None, None, None, Q, K, V, (None, None, gamma_q, gamma_k), (None, None, cos, sin), eps,
+                    None, O, workspace, stream)
+
 
 class JointAttention(_Module):
     """Mirror of f2k::cuda::JointAttention: attention over text tokens followed by image tokens."""
@@ -106,9 +170,6 @@ class JointAttention(_Module):
     def workspace_size_bytes(self) -> int:
         return int(lib.f2k_attn_workspace_bytes(self._h)) if self.ok() else 0
 
-    def fused_workspace_size_bytes(self) -> int:
-        return int(lib.f2k_attn_fused_workspace_bytes(self._h)) if self.ok() else 0
-
     def forward(self, Q_txt, K_txt, V_txt, Q_img, K_img, V_img, O_txt, O_img,
                 workspace=None, workspace_size=0, stream=None) -> bool:
         if not self.ok():
@@ -117,31 +178,6 @@ class JointAttention(_Module):
         return lib.f2k_attn_forward(self._h, _p(Q_txt), _p(K_txt), _p(V_txt), _p(Q_img), _p(K_img),
                                     _p(V_img), _p(O_txt), _p(O_img), _p(workspace), workspace_size,
                                     _stream(stream)) == _lib.F2K_OK
-
-    def forward_fused(self, Q_txt, K_txt, V_txt, Q_img, K_img, V_img, gammas, tables, eps,
-                      O_txt, O_img, workspace, stream=None) -> bool:
-        """Raw projections in; per-head RMSNorm + RoPE + attention in one call.
-        gammas = (gq_txt, gk_txt, gq_img, gk_img) bf16 [128];
-        tables = (cos_txt, sin_txt, cos_img, sin_img) fp32 [seq, 64]."""
-        if not self.ok():
-            return False
-        _check_bf16(Q_txt, K_txt, V_txt, Q_img, K_img, V_img, O_txt, O_img, *gammas)
-        ws_bytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
-        return lib.f2k_attn_forward_fused(
-            self._h, _p(Q_txt), _p(K_txt), _p(V_txt), _p(Q_img), _p(K_img), _p(V_img),
-            *[_p(g) for g in gammas], *[_p(t) for t in tables], eps, _p(O_txt), _p(O_img),
-            _p(workspace), ws_bytes, _stream(stream)) == _lib.F2K_OK
-
-    def forward_fused_host(self, hQ_txt, hK_txt, hV_txt, hQ_img, hK_img, hV_img, gammas, tables,
-                           eps, hO_txt, hO_img, stream=None) -> bool:
-        """Same as forward_fused with q, k, v, o in (pinned) host memory; gammas and tables on
-        the GPU. Asynchronous on the stream."""
-        if not self.ok():
-            return False
-        return lib.f2k_attn_forward_fused_host(
-            self._h, _p(hQ_txt), _p(hK_txt), _p(hV_txt), _p(hQ_img), _p(hK_img), _p(hV_img),
-            *[_p(g) for g in gammas], *[_p(t) for t in tables], eps, _p(hO_txt), _p(hO_img),
-            _stream(stream)) == _lib.F2K_OK
 
 
 def rmsnorm_bf16(x, gamma, y, batch_rows: int, dim: int, eps: float, stream=None) -> bool:

@@ -18,6 +18,7 @@ cudaError_t attn_fwd_launch(const AttnParams& p, cudaStream_t stream);
 // launch (qk_prologue.cu). One job per tensor; all jobs share head count and eps.
 struct QkPrologueJob {
     const void*  x;        // [batch, seq, heads, 128] bf16, raw projection output
+    long long    x_tok_stride;  // elements between two token rows of x (0 = dense, heads * 128)
     void*        y;        // same shape; may equal x
     const void*  gamma;    // [128] bf16
     const float* cos_tab;  // [seq, 64] fp32

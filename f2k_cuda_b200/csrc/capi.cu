@@ -86,6 +86,7 @@ struct f2k_attn {
     // Descriptors of the last forward call; rebuilt only when a pointer changes.
     const void* last_in[6] = {};
     void*       last_out[2] = {};
+    long long   last_vo[4] = {};
     bool        have_params = false;
     AttnParams  params;
 
@@ -120,8 +121,9 @@ int fail_cuda(f2k_attn* h, const char* what, cudaError_t e) {
     return fail(h, F2K_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
 }
 
-struct QSeg  { const void* q; void* o; int len; };
-struct KvSeg { const void* k; const void* v; int len; };
+// token strides in elements; 0 = dense (heads * 128)
+struct QSeg  { const void* q; void* o; int len; long long q_stride = 0, o_stride = 0; };
+struct KvSeg { const void* k; const void* v; int len; long long k_stride = 0, v_stride = 0; };
 
 // Launch parameters for attention of the given query segments over the given key/value segments;
 // every segment is bf16 [batch, len, heads, 128], dense.
@@ -136,11 +138,12 @@ int build_params(f2k_attn* h, AttnParams& p, const QSeg* qs, int nq, const KvSeg
         if (!g.q || !g.o) return fail(h, F2K_ERR_INVALID, "null tensor pointer");
         if ((reinterpret_cast<uintptr_t>(g.o) & 15u) != 0)
             return fail(h, F2K_ERR_INVALID, "output pointer is not 16-byte aligned");
-        const long long bstride = (long long)g.len * tok;
-        if (!encode_segment(&p.tm_q[s], g.q, g.len, c.n_heads, c.batch, tok, bstride, h->err)) return F2K_ERR_CUDA;
+        const long long qs_ = g.q_stride ? g.q_stride : tok, os_ = g.o_stride ? g.o_stride : tok;
+        if (!encode_segment(&p.tm_q[s], g.q, g.len, c.n_heads, c.batch, qs_, (long long)g.len * qs_, h->err))
+            return F2K_ERR_CUDA;
         p.o_ptr[s]          = g.o;
-        p.o_tok_stride[s]   = tok;
-        p.o_batch_stride[s] = bstride;
+        p.o_tok_stride[s]   = os_;
+        p.o_batch_stride[s] = (long long)g.len * os_;
         p.q_len[s]          = g.len;
         p.q_tile_start[s]   = tiles;
         tiles += (g.len + kTileM - 1) / kTileM;
@@ -152,9 +155,9 @@ int build_params(f2k_attn* h, AttnParams& p, const QSeg* qs, int nq, const KvSeg
     for (int s = 0; s < nkv; ++s) {
         const KvSeg& g = kvs[s];
         if (!g.k || !g.v) return fail(h, F2K_ERR_INVALID, "null tensor pointer");
-        const long long bstride = (long long)g.len * tok;
-        if (!encode_segment(&p.tm_k[s], g.k, g.len, c.n_heads, c.batch, tok, bstride, h->err) ||
-            !encode_segment(&p.tm_v[s], g.v, g.len, c.n_heads, c.batch, tok, bstride, h->err))
+        const long long ks_ = g.k_stride ? g.k_stride : tok, vs_ = g.v_stride ? g.v_stride : tok;
+        if (!encode_segment(&p.tm_k[s], g.k, g.len, c.n_heads, c.batch, ks_, (long long)g.len * ks_, h->err) ||
+            !encode_segment(&p.tm_v[s], g.v, g.len, c.n_heads, c.batch, vs_, (long long)g.len * vs_, h->err))
             return F2K_ERR_CUDA;
         p.kv_len[s]        = g.len;
         p.kv_tile_start[s] = tiles;
@@ -172,13 +175,16 @@ int build_params(f2k_attn* h, AttnParams& p, const QSeg* qs, int nq, const KvSeg
 
 // Builds (or reuses) the launch parameters for attention over the text||image
 // segments held at the given pointers.
+// vo_strides: token strides of v_txt, o_txt, v_img, o_img (0 = dense); Q and K are dense here.
 int prepare_params(f2k_attn* h, const void* q_txt, const void* k_txt, const void* v_txt,
                    const void* q_img, const void* k_img, const void* v_img, void* o_txt,
-                   void* o_img) {
+                   void* o_img, const long long* vo_strides = nullptr) {
     const void* in[6] = {q_txt, k_txt, v_txt, q_img, k_img, v_img};
     void* out[2]      = {o_txt, o_img};
+    long long vo[4]   = {0, 0, 0, 0};
+    if (vo_strides) std::memcpy(vo, vo_strides, sizeof vo);
     if (h->have_params && std::memcmp(in, h->last_in, sizeof in) == 0 &&
-        std::memcmp(out, h->last_out, sizeof out) == 0)
+        std::memcmp(out, h->last_out, sizeof out) == 0 && std::memcmp(vo, h->last_vo, sizeof vo) == 0)
         return F2K_OK;
     h->have_params = false;
     const f2k_attn_config& c = h->cfg;
@@ -186,12 +192,12 @@ int prepare_params(f2k_attn* h, const void* q_txt, const void* k_txt, const void
     KvSeg kvs[2];
     int n = 0;
     if (c.seq_txt > 0) {
-        qs[n]  = {q_txt, o_txt, c.seq_txt};
-        kvs[n] = {k_txt, v_txt, c.seq_txt};
+        qs[n]  = {q_txt, o_txt, c.seq_txt, 0, vo[1]};
+        kvs[n] = {k_txt, v_txt, c.seq_txt, 0, vo[0]};
         ++n;
     }
-    qs[n]  = {q_img, o_img, c.seq_img};
-    kvs[n] = {k_img, v_img, c.seq_img};
+    qs[n]  = {q_img, o_img, c.seq_img, 0, vo[3]};
+    kvs[n] = {k_img, v_img, c.seq_img, 0, vo[2]};
     ++n;
     for (int i = 0; i < n; ++i)
         if (!qs[i].q || !kvs[i].k || !kvs[i].v || !qs[i].o) return fail(h, F2K_ERR_INVALID, "null tensor pointer");
@@ -199,6 +205,7 @@ int prepare_params(f2k_attn* h, const void* q_txt, const void* k_txt, const void
     if (rc != F2K_OK) return rc;
     std::memcpy(h->last_in, in, sizeof in);
     std::memcpy(h->last_out, out, sizeof out);
+    std::memcpy(h->last_vo, vo, sizeof vo);
     h->have_params = true;
     return F2K_OK;
 }
@@ -429,12 +436,37 @@ int f2k_attn_forward_fused(f2k_attn* h, const void* q_txt, const void* k_txt, co
                            const float* sin_txt, const float* cos_img, const float* sin_img,
                            float eps, void* o_txt, void* o_img, void* workspace,
                            size_t workspace_bytes, void* stream) {
+    return f2k_attn_forward_fused_strided(h, q_txt, k_txt, v_txt, q_img, k_img, v_img, gamma_q_txt, gamma_k_txt,
+                                          gamma_q_img, gamma_k_img, cos_txt, sin_txt, cos_img, sin_img, eps, o_txt,
+                                          o_img, nullptr, workspace, workspace_bytes, stream);
+}
+
+int f2k_attn_forward_fused_strided(f2k_attn* h, const void* q_txt, const void* k_txt, const void* v_txt,
+                                   const void* q_img, const void* k_img, const void* v_img,
+                                   const void* gamma_q_txt, const void* gamma_k_txt,
+                                   const void* gamma_q_img, const void* gamma_k_img, const float* cos_txt,
+                                   const float* sin_txt, const float* cos_img, const float* sin_img,
+                                   float eps, void* o_txt, void* o_img, const f2k_attn_strides* strides,
+                                   void* workspace, size_t workspace_bytes, void* stream) {
     if (!h) return F2K_ERR_INVALID;
     if (!h->valid) return F2K_ERR_INVALID;
     if (workspace_bytes < h->fused_ws() || !workspace)
         return fail(h, F2K_ERR_WORKSPACE, "workspace too small");
     const f2k_attn_config& c = h->cfg;
     const bool has_txt = c.seq_txt > 0;
+    f2k_attn_strides st{};
+    if (strides) {
+        st = *strides;
+        const long long dense = (long long)c.n_heads * kHeadDim;
+        const long long all[8] = {st.q_txt, st.k_txt, st.v_txt, st.o_txt, st.q_img, st.k_img, st.v_img, st.o_img};
+        for (long long v : all)
+            if (v != 0 && (v < dense || v % 8 != 0))
+                return fail(h, F2K_ERR_INVALID, "token stride must be 0 or a multiple of 8 that is >= n_heads * 128");
+        const void* raw[4] = {q_txt, k_txt, q_img, k_img};
+        for (const void* ptr : raw)
+            if ((reinterpret_cast<uintptr_t>(ptr) & 15u) != 0)
+                return fail(h, F2K_ERR_INVALID, "tensor base pointer is not 16-byte aligned");
+    }
     if (!q_img || !k_img || !gamma_q_img || !gamma_k_img || !cos_img || !sin_img ||
         (has_txt && (!q_txt || !k_txt || !gamma_q_txt || !gamma_k_txt || !cos_txt || !sin_txt)))
         return fail(h, F2K_ERR_INVALID, "null tensor pointer");
@@ -449,27 +481,29 @@ int f2k_attn_forward_fused(f2k_attn* h, const void* q_txt, const void* k_txt, co
     std::memset(&pp, 0, sizeof pp);
     int n = 0;
     long long rows = 0;
-    auto add = [&](const void* x, void* y, const void* g, const float* ct, const float* st, int seq) {
+    auto add = [&](const void* x, long long x_stride, void* y, const void* g, const float* ct, const float* sn,
+                   int seq) {
         QkPrologueJob& j = pp.job[n];
-        j.x = x; j.y = y; j.gamma = g; j.cos_tab = ct; j.sin_tab = st; j.seq = seq;
+        j.x = x; j.x_tok_stride = x_stride; j.y = y; j.gamma = g; j.cos_tab = ct; j.sin_tab = sn; j.seq = seq;
         j.rows = (long long)c.batch * seq * c.n_heads;
         pp.row_start[n] = rows;
         rows += j.rows;
         ++n;
     };
     if (has_txt) {
-        add(q_txt, qn_txt, gamma_q_txt, cos_txt, sin_txt, c.seq_txt);
-        add(k_txt, kn_txt, gamma_k_txt, cos_txt, sin_txt, c.seq_txt);
+        add(q_txt, st.q_txt, qn_txt, gamma_q_txt, cos_txt, sin_txt, c.seq_txt);
+        add(k_txt, st.k_txt, kn_txt, gamma_k_txt, cos_txt, sin_txt, c.seq_txt);
     }
-    add(q_img, qn_img, gamma_q_img, cos_img, sin_img, c.seq_img);
-    add(k_img, kn_img, gamma_k_img, cos_img, sin_img, c.seq_img);
+    add(q_img, st.q_img, qn_img, gamma_q_img, cos_img, sin_img, c.seq_img);
+    add(k_img, st.k_img, kn_img, gamma_k_img, cos_img, sin_img, c.seq_img);
     pp.row_start[n] = rows;
     pp.n_jobs  = n;
     pp.n_heads = c.n_heads;
     pp.eps     = eps;
 
+    const long long vo[4] = {st.v_txt, st.o_txt, st.v_img, st.o_img};
     const int rc = prepare_params(h, has_txt ? qn_txt : nullptr, has_txt ? kn_txt : nullptr, v_txt,
-                                  qn_img, kn_img, v_img, o_txt, o_img);
+                                  qn_img, kn_img, v_img, o_txt, o_img, vo);
     if (rc != F2K_OK) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     cudaError_t e = qk_prologue_launch(pp, s);

@@ -96,9 +96,13 @@ qk_prologue_kernel(const __grid_constant__ QkPrologueParams p) {
             if (i < p.n_jobs && row >= p.row_start[i]) j = i;
         const QkPrologueJob& job = p.job[j];
         const long long lr = row - p.row_start[j];
-        const int tok = (int)((lr / p.n_heads) % job.seq);
-        // plain loads of x: y may alias x, so x is not read-only for the kernel's lifetime
-        const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(job.x) + lr * kHeadDim);
+        const long long trow = lr / p.n_heads;                 // token row over batch * seq
+        const int tok = (int)(trow % job.seq);
+        const int hd0 = (int)(lr - trow * p.n_heads);           // first head of the group
+        // plain loads of x: y may alias x, so x is not read-only for the kernel's lifetime. A token
+        // row of x may be a slice of a wider row (x_tok_stride); y is always dense.
+        const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(job.x) +
+                                                          trow * job.x_tok_stride + (long long)hd0 * kHeadDim);
         uint4 raw[kGroup];
 #pragma unroll
         for (int u = 0; u < kGroup; ++u) raw[u] = src[u * 16 + hl];
@@ -267,7 +271,10 @@ cudaError_t qk_prologue_prepare() {
     return e;
 }
 
-cudaError_t qk_prologue_launch(const QkPrologueParams& p, cudaStream_t stream) {
+cudaError_t qk_prologue_launch(const QkPrologueParams& params, cudaStream_t stream) {
+    QkPrologueParams p = params;
+    for (int i = 0; i < p.n_jobs; ++i)
+        if (p.job[i].x_tok_stride == 0) p.job[i].x_tok_stride = (long long)p.n_heads * kHeadDim;
     const long long total = p.row_start[p.n_jobs];
     if (total <= 0) return cudaSuccess;
     if (p.n_heads % 4 == 0)

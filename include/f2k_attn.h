@@ -102,6 +102,35 @@ int f2k_attn_forward_fused(f2k_attn* h,
                            void* o_txt, void* o_img,
                            void* workspace, size_t workspace_bytes, void* stream);
 
+/* Token strides, in elements, for a fused call whose tensor rows are not dense. A token row of
+ * Q, K or V may be a slice of a wider row - the fused QKV(+MLP) projection output of the
+ * reference's single-stream block, 36864 elements per token, which the reference first splits
+ * with split_qkv_mlp_kernel (src/backend/cuda/kernels/qkv_mlp_split.cu:12-42) - and a row of O
+ * a slice of the [attn | mlp] buffer it otherwise fills with concat_attn_mlp_kernel (same file,
+ * :44-57; 16384 elements per token). 0 = dense (n_heads * 128). Rows of all batch elements are
+ * consecutive: token (b, s) starts at (b * seq + s) * stride. Every stride must be a multiple
+ * of 8 and at least n_heads * 128; every base pointer 16-byte aligned. */
+typedef struct f2k_attn_strides {
+    long long q_txt, k_txt, v_txt, o_txt;
+    long long q_img, k_img, v_img, o_img;
+} f2k_attn_strides;
+
+/* f2k_attn_forward_fused on strided rows (strides NULL = all dense): reads Q, K, V where the
+ * projection left them and writes O where the next layer wants it, so that the reference's
+ * split and concat copies around the attention (single_stream_block.cu:247-250, 272-274)
+ * are not needed. The normalised Q/K copies in the workspace stay dense. */
+int f2k_attn_forward_fused_strided(f2k_attn* h,
+                                   const void* q_txt, const void* k_txt, const void* v_txt,
+                                   const void* q_img, const void* k_img, const void* v_img,
+                                   const void* gamma_q_txt, const void* gamma_k_txt,
+                                   const void* gamma_q_img, const void* gamma_k_img,
+                                   const float* cos_txt, const float* sin_txt,
+                                   const float* cos_img, const float* sin_img,
+                                   float eps,
+                                   void* o_txt, void* o_img,
+                                   const f2k_attn_strides* strides,
+                                   void* workspace, size_t workspace_bytes, void* stream);
+
 /* Same computation as f2k_attn_forward_fused with q, k, v, o in HOST memory (pinned
  * memory makes the copies asynchronous); gains and tables stay device pointers, like
  * the construction-time uploads of the reference. Never synchronises: the call starts

@@ -327,3 +327,68 @@ def test_host_buffer_entry_point(f2k, orc, monkeypatch, batch, heads, mode):
     assert ja.device_status() == 0
     d_t, d_i = run_joint(f2k, (p.q_txt, p.k_txt, p.v_txt), (p.q_img, p.k_img, p.v_img), fused=(p.gammas, tabs))
     assert np.array_equal(host_f32(ho_t), d_t) and np.array_equal(host_f32(ho_i), d_i)
+
+
+@pytest.mark.parametrize("batch,seq_txt,heads", [(1, 0, 8), (2, 64, 4)])
+def test_strided_rows_read_the_projection_output_in_place(f2k, batch, seq_txt, heads):
+    """Q, K, V as column slices of one wide projection buffer (the reference's fused QKV+MLP
+    output, which it first splits) and O as a column slice of the [attn | mlp] buffer: same bits as
+    the dense call on contiguous copies, and nothing outside the O columns is written."""
+    import torch
+    from f2k_cuda_b200.inputs import Workload, make_problem
+    w = Workload("strided", batch, seq_txt, ((16, 24),), seed=0x57D1)
+    p = make_problem(w, heads=heads)
+    hd = heads * 128
+    wide, out_w = 3 * hd + 520, hd + 264            # row widths, multiples of 8
+    tabs = (*f2k.build_rope_4axis_tables((32,) * 4, p.pos_txt, 2000.0),
+            *f2k.build_rope_4axis_tables((32,) * 4, p.pos_img, 2000.0))
+    dg = [dev_bf16(g) for g in p.gammas]
+    dtab = [torch.from_numpy(x).cuda() for x in tabs]
+    ja = (f2k.JointAttention(f2k.JointAttention.Config(batch, seq_txt, w.seq_img, heads, 128)) if seq_txt
+          else f2k.Attention(f2k.Attention.Config(batch, w.seq_img, heads, 128)))
+    assert ja.ok(), ja.last_error()
+    ws = torch.empty(ja.fused_workspace_size_bytes(), dtype=torch.uint8, device="cuda")
+
+    def stream_views(q, k, v):
+        S = q.shape[1]
+        proj = torch.full((batch * S, wide), 7.0, dtype=torch.bfloat16, device="cuda")
+        out = torch.full((batch * S, out_w), -3.0, dtype=torch.bfloat16, device="cuda")
+        views = []
+        for i, x in enumerate((q, k, v)):
+            proj[:, i * hd:(i + 1) * hd] = dev_bf16(x).reshape(batch * S, hd)
+            views.append(proj[:, i * hd:(i + 1) * hd].unflatten(0, (batch, S)).unflatten(2, (heads, 128)))
+        o = out[:, 8:8 + hd].unflatten(0, (batch, S)).unflatten(2, (heads, 128))
+        return views, o, out
+
+    (vi, o_i, out_i) = stream_views(p.q_img, p.k_img, p.v_img)
+    if seq_txt:
+        (vt, o_t, out_t) = stream_views(p.q_txt, p.k_txt, p.v_txt)
+    else:
+        vt, o_t, out_t = [None] * 3, None, None
+    g = dg if seq_txt else [None, None, dg[2], dg[3]]
+    t = dtab if seq_txt else [None, None, dtab[2], dtab[3]]
+    assert ja.forward_fused_strided(*vt, *vi, g, t, 1e-6, o_t, o_i, ws), ja.last_error()
+    torch.cuda.synchronize()
+    assert ja.device_status() == 0
+    # dense call on contiguous copies
+    di = [dev_bf16(x) for x in (p.q_img, p.k_img, p.v_img)]
+    dt = [dev_bf16(x) for x in (p.q_txt, p.k_txt, p.v_txt)] if seq_txt else [None] * 3
+    r_i = torch.empty_like(di[0])
+    r_t = torch.empty_like(dt[0]) if seq_txt else None
+    assert ja.forward_fused(*dt, *di, g, t, 1e-6, r_t, r_i, ws), ja.last_error()
+    torch.cuda.synchronize()
+    assert torch.equal(o_i, r_i)
+    assert bool((out_i[:, :8] == -3.0).all()) and bool((out_i[:, 8 + hd:] == -3.0).all())
+    if seq_txt:
+        assert torch.equal(o_t, r_t)
+        assert bool((out_t[:, :8] == -3.0).all()) and bool((out_t[:, 8 + hd:] == -3.0).all())
+    # refusals: a stride that is not a multiple of 8, or smaller than a dense row
+    import ctypes as C
+    from f2k_cuda_b200 import _lib
+    bad = _lib.AttnStrides(q_img=hd + 4)
+    rc = _lib.lib.f2k_attn_forward_fused_strided(
+        ja._h, *[None if x is None else C.c_void_p(x.data_ptr()) for x in (*dt, *di)],
+        *[None if x is None else C.c_void_p(x.data_ptr()) for x in (*g, *t)], 1e-6,
+        None if r_t is None else C.c_void_p(r_t.data_ptr()), C.c_void_p(r_i.data_ptr()), C.byref(bad),
+        C.c_void_p(ws.data_ptr()), ws.numel(), None)
+    assert rc == _lib.F2K_ERR_INVALID and "stride" in ja.last_error()
