@@ -55,10 +55,12 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="s4608",
-                    choices=["s4608", "s8704_seqpar", "s16896_seqpar", "s4608_b4_heads", "s8704_heads", "s16896_heads"],
+                    choices=["s4608", "s8704_seqpar", "s16896_seqpar", "s4608_b4_heads", "s8704_heads", "s16896_heads",
+                             "s8704_hx", "s16896_hx"],
                     help="s4608: the headline shape (heads sharded over the GPUs, batch grows with N). *_seqpar: the "
                          "long shapes with the sequence sharded over the GPUs (strong scaling, K/V pulled over NVLink "
-                         "under the kernel). *_heads: a fixed job with its 32 heads sharded 32/N per GPU (strong scaling)")
+                         "under the kernel). *_heads: a fixed job with its 32 heads sharded 32/N per GPU (strong scaling). "
+                         "*_hx: sequence sharded outside, heads sharded inside (head exchange by peer stores)")
     ap.add_argument("--no-overlap", action="store_true", help="seqpar: start the kernel only after all K/V pulls")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the timed CPU leg")
     ap.add_argument("--no-reference-kernel", action="store_true",
@@ -522,6 +524,81 @@ def run_heads_strong(args, rank, world):
     }
 
 
+def run_headswap(args, rank, world):
+    """Sequence-parallel attention by head exchange on the 8704- / 16896-token shapes, batch 1, 32
+    heads: every rank owns S/world tokens outside and 32/world heads inside. Step = one kernel that
+    normalises + rotates Q, K and scatters Q, K, V by head into the peers' memory, the attention
+    kernel (its epilogue stores each output row into the token owner's memory), and the wait for the
+    other ranks' rows. Strong scaling; no collective and no copy engine in the step."""
+    import f2k_cuda_b200 as f2k
+    from f2k_cuda_b200.headswap import HeadExchangeAttention
+    from f2k_cuda_b200.inputs import WORKLOADS, make_problem, token_positions
+    w = WORKLOADS["s16896" if args.workload.startswith("s16896") else "s8704_edit"]
+    S, H, D = w.seq, w.n_heads, w.head_dim
+    if S % world != 0 or H % world != 0:
+        raise SystemExit(f"{S} tokens / {H} heads do not split evenly over {world} ranks")
+    per = S // world
+    b, e = rank * per, (rank + 1) * per
+    stream = torch.cuda.current_stream()
+    pt, pi = token_positions(w)
+    cos_t, sin_t = f2k.build_rope_4axis_tables((32,) * 4, pt, 2000.0)
+    cos_i, sin_i = f2k.build_rope_4axis_tables((32,) * 4, pi, 2000.0)
+    dcos = torch.from_numpy(np.concatenate([cos_t, cos_i])[b:e].copy()).cuda()
+    dsin = torch.from_numpy(np.concatenate([sin_t, sin_i])[b:e].copy()).cuda()
+    gen = torch.Generator(device="cuda").manual_seed(1234 + rank)
+    mk = lambda: torch.randn(1, per, H, D, device="cuda", generator=gen).to(torch.bfloat16)  # noqa: E731
+    q_raw, k_raw, v = mk(), mk(), mk()
+    g = [dev_bf16(x) for x in make_problem(WORKLOADS["s1152"], heads=1).gammas]
+    hx = HeadExchangeAttention(per, H, D, world, rank)
+    if not hx.ok():
+        raise RuntimeError(hx.last_error())
+    ok = hx.attach_distributed() if world > 1 else hx.attach_in_process([hx])
+    if not ok:
+        raise RuntimeError("attaching the peers' exchange buffers failed: " + hx.last_error())
+    if world > 1:
+        torch.distributed.barrier()
+
+    def step():
+        # one gain pair for the whole sequence (the single-stream block's call)
+        if not (hx.exchange_in(q_raw, k_raw, v, g[2], g[3], dcos, dsin, 1e-6) and hx.attend()) or hx.output() is None:
+            raise RuntimeError(hx.last_error())
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    if hx.device_status() != 0:
+        raise RuntimeError("attention kernel reported a device-side error during warm-up")
+    sampler = ClockSampler(torch.cuda.current_device()) if rank == 0 else None
+    if world > 1:
+        torch.distributed.barrier()
+    ms = time_region(step, args.steps, stream)
+    if world > 1:
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        ms = float(t.item())
+    clocks = sampler.stop() if sampler else None
+    if hx.device_status() != 0:
+        raise RuntimeError("attention kernel reported a device-side error")
+    if rank != 0:
+        return None
+    flops = 4.0 * H * float(S) ** 2 * D                # whole job
+    peak, peak_src = measured_peak()
+    return {
+        "metric": METRIC, "value": flops / (ms * 1e-3) / 1e12, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"{w.name}: {S} tokens, batch 1, 32 heads, hd128, {per} tokens per GPU outside, "
+                               f"{H // world} heads per GPU inside",
+                   "step": "QK-RMSNorm + RoPE + head scatter into peer memory (one kernel); attention with the "
+                           "epilogue storing into the token owner's memory; wait for the peers' rows",
+                   "flops_per_step_total": flops, "parallelism": f"headswap{world}",
+                   "nvlink_bytes_per_gpu_per_step": 4 * (world - 1) * per * (H // world) * D * 2,
+                   "l2": "Q, K, V, O of a step (%.0f MB per GPU) exceed the 126 MB L2" % (4 * S * (H // world) * D * 2 / 1e6)},
+        "per_gpu_tflops": flops / world / (ms * 1e-3) / 1e12,
+        "pct_of_peak": 100.0 * flops / world / (ms * 1e-3) / 1e12 / peak, "peak_source": peak_src,
+        "e2e": None, "gpu_launches": 2 * args.steps, "clocks": clocks,
+    }
+
+
 def run_reference(args, rank, world):
     """The reference's own implementation of the path: its CUDA kernels (rmsnorm_bf16 x4,
     rope_4axis_inplace_bf16 x4, JointAttention::forward with its concat/split copies), rebuilt
@@ -652,6 +729,8 @@ def main():
             line = run_ours(args, rank, world)
         elif args.workload.endswith("_heads"):
             line = run_heads_strong(args, rank, world)
+        elif args.workload.endswith("_hx"):
+            line = run_headswap(args, rank, world)
         else:
             line = run_seqpar(args, rank, world)
         if line is not None:

@@ -76,6 +76,24 @@ def _declare(lib: C.CDLL) -> None:
     lib.f2k_seqpar_forward.argtypes = [vp, vp, vp, i, vp, vp]
     lib.f2k_seqpar_device_status.restype = i
     lib.f2k_seqpar_device_status.argtypes = [vp, C.POINTER(i)]
+    lib.f2k_hx_create.restype = i
+    lib.f2k_hx_create.argtypes = [C.POINTER(SeqParConfig), C.POINTER(vp)]
+    lib.f2k_hx_destroy.restype = None
+    lib.f2k_hx_destroy.argtypes = [vp]
+    lib.f2k_hx_last_error.restype = C.c_char_p
+    lib.f2k_hx_last_error.argtypes = [vp]
+    lib.f2k_hx_buffer.restype = i
+    lib.f2k_hx_buffer.argtypes = [vp, C.POINTER(vp), C.POINTER(sz)]
+    lib.f2k_hx_attach.restype = i
+    lib.f2k_hx_attach.argtypes = [vp, C.POINTER(vp)]
+    lib.f2k_hx_exchange_in.restype = i
+    lib.f2k_hx_exchange_in.argtypes = [vp] * 8 + [f, vp]
+    lib.f2k_hx_attend.restype = i
+    lib.f2k_hx_attend.argtypes = [vp, vp]
+    lib.f2k_hx_output.restype = i
+    lib.f2k_hx_output.argtypes = [vp, C.POINTER(vp), vp]
+    lib.f2k_hx_device_status.restype = i
+    lib.f2k_hx_device_status.argtypes = [vp, C.POINTER(i)]
     lib.f2k_ipc_export.restype = i
     lib.f2k_ipc_export.argtypes = [vp, vp]
     lib.f2k_ipc_open.restype = i

@@ -17,7 +17,7 @@ CSRC = PKG_DIR / "csrc"
 BUILD_DIR = PKG_DIR / "_build"
 LIB_PATH = BUILD_DIR / "libf2k_attn.so"
 
-SOURCES = ["attn_fwd_sm100.cu", "qk_prologue.cu", "capi.cu", "no_alloc.cu", "seqpar.cu", "f2k_compat.cpp"]
+SOURCES = ["attn_fwd_sm100.cu", "qk_prologue.cu", "capi.cu", "no_alloc.cu", "seqpar.cu", "headswap.cu", "f2k_compat.cpp"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

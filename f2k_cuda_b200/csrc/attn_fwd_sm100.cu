@@ -225,11 +225,16 @@ attn_fwd_sm100_kernel(const __grid_constant__ AttnParams p) {
                 int issued = 0;
                 bool ok = true;
                 PH_EVDECL(300);
-                for (int t = 0; t < 2; ++t) {
+                for (int t = 0; t < 2 && ok; ++t) {
                     const int qt = 2 * pair + t;
                     int seg, row0, valid;
                     if (qt < p.n_q_tiles) {
                         locate_tile<kMaxQSeg>(p.q_tile_start, p.q_len, p.n_qseg, qt, seg, row0, valid);
+                        if (p.q_ready[seg] != nullptr) {   // the segment is written by another GPU's kernel
+                            ok = global_flag_wait(p.q_ready[seg], p.kv_ready_value, abort_flag);
+                            if (!ok) break;
+                            asm volatile("fence.proxy.async.global;" ::: "memory");
+                        }
                     } else {  // odd tile count: the spare tile reads zeros (out of bounds)
                         seg = 0;
                         row0 = ((p.q_len[0] + kTileM - 1) / kTileM) * kTileM;
@@ -537,6 +542,8 @@ attn_fwd_sm100_kernel(const __grid_constant__ AttnParams p) {
     __syncthreads();
     if (threadIdx.x == 0 && *abort_flag != 0u && p.status != nullptr)
         atomicOr(p.status, (int)kStatusWaitExpired);
+    if (threadIdx.x == 0 && p.done_counter != nullptr)   // all output rows of this CTA are stored (barrier above)
+        grid_done_publish(p.done_counter, gridDim.x * gridDim.y * gridDim.z, p.done_flag, p.n_done, p.done_value);
     if (warp == kMmaWarp) {
         tc_fence_after_sync();
         tmem_dealloc(tmem, kTmemCols);

@@ -37,6 +37,24 @@ struct QkPrologueParams {
 cudaError_t qk_prologue_launch(const QkPrologueParams& p, cudaStream_t stream);
 cudaError_t qk_prologue_prepare();   // load the prologue kernels on the current device
 
+// Head exchange (qk_prologue.cu): the prologue of a rank that holds `s_loc` tokens of all heads,
+// writing every head row straight into the memory of the rank that attends that head. Q and K
+// are normalised and rotated on the way, V is copied. Destination layout on rank r:
+// [world * s_loc tokens, heads_per_rank, 128], this rank's tokens at token offset rank * s_loc.
+// The last CTA then stores `value` to flag[0 .. world) (one word per destination rank).
+struct QkvScatterParams {
+    const void*  q; const void* k; const void* v;          // [s_loc, n_heads, 128] bf16, dense
+    const void*  gamma_q; const void* gamma_k;             // [128] bf16
+    const float* cos_tab; const float* sin_tab;            // [s_loc, 64] fp32 (this rank's rows)
+    unsigned char* dst_q[8]; unsigned char* dst_k[8]; unsigned char* dst_v[8];
+    unsigned int*  flag[8];
+    unsigned int*  counter;                                // zero before the launch, zero after
+    unsigned int   value;
+    int   s_loc, n_heads, heads_per_rank, world, rank;
+    float eps;
+};
+cudaError_t qkv_scatter_launch(const QkvScatterParams& p, cudaStream_t stream);
+
 // Stand-alone kernels with the reference's call shapes (qk_prologue.cu).
 cudaError_t rmsnorm_rows_launch(const void* x, const void* gamma, void* y, int rows, int dim,
                                 float eps, cudaStream_t stream);

@@ -17,7 +17,7 @@ namespace f2k {
 constexpr int kHeadDim  = 128;  // the only head_dim the MMDiT path uses
 constexpr int kTileM    = 128;  // query rows per tile (one TMEM lane each)
 constexpr int kTileN    = 128;  // keys per tile
-constexpr int kMaxQSeg  = 4;
+constexpr int kMaxQSeg  = 8;
 constexpr int kMaxKvSeg = 8;
 
 // Bits of the device status word a launch may set (0 = clean run).
@@ -62,6 +62,21 @@ struct AttnParams {
     const unsigned int* kv_ready[kMaxKvSeg];
     unsigned int        kv_ready_value;
     int                 kv_ready_heads_per_group;
+
+    // Head-exchange use (tokens sharded outside the attention, heads inside): query segment i is
+    // written into this GPU's memory by rank i's kernel, which then stores kv_ready_value (or a
+    // later call's value) to q_ready[i]; the TMA producer waits for that word, bounded, before it
+    // fetches a query tile of the segment. Null for data that is already in place.
+    const unsigned int* q_ready[kMaxQSeg];
+
+    // When done_counter is not null, the last CTA to finish stores done_value to each of the
+    // n_done words done_flag[] (words in this and in the peers' memory) after every output row of
+    // the launch has been written: outputs may go straight into other GPUs' buffers (o_ptr), and
+    // this tells their owners. The counter is left at zero for the next launch.
+    unsigned int* done_counter;
+    unsigned int* done_flag[8];
+    int           n_done;
+    unsigned int  done_value;
 };
 
 }  // namespace f2k

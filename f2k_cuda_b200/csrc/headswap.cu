@@ -1,0 +1,284 @@
+// Token-sharded in, token-sharded out, heads sharded inside: sequence-parallel attention by head
+// exchange over NVLink peer memory ("all-to-all" form). The reference has no multi-GPU code; this
+// layer is new, and is the low-traffic alternative to the ring of seqpar.cu: per step a GPU sends
+// and receives 4 * (world-1)/world shards instead of 2 * (world-1) shards.
+//
+// Rank r holds Q, K, V of its s_loc tokens, all heads. Per step:
+//
+//  1. exchange_in: ONE kernel (qkv_scatter_kernel) reads the rank's raw Q, K, V once, applies
+//     QK-RMSNorm + RoPE to Q and K, and stores every head row directly into the memory of the rank
+//     that owns the head (peer stores): rank d receives [world * s_loc tokens, heads/world, 128]
+//     for Q, K and V. Its last CTA publishes an "arrived" word on every rank.
+//  2. attend: the attention kernel over heads/world heads and all tokens. Its TMA producer waits
+//     (bounded) for the "arrived" word of a source rank before the first tile of that rank's
+//     token range, so it starts on what has arrived. Queries are cut into one segment per
+//     source rank, and a segment's output pointer is the SOURCE rank's token-sharded output
+//     buffer: the epilogue's stores are the exchange back. The last CTA publishes "done".
+//  3. output: stream waits for every rank's "done" word; the rank's [s_loc, heads, 128] output
+//     is then complete in its own buffer.
+//
+// No collective, no copy engine, no kernel that spins on another kernel's progress on the same
+// GPU (waits are on words written by other GPUs). Two buffer sets alternate from step to step; a
+// peer can be at most one step ahead, because its next exchange needs this rank's "arrived".
+//
+// One allocation per rank, exported to the peers by CUDA IPC:
+//     [2 sets] { Qh, Kh, Vh : [world * s_loc, heads/world, 128] ; O : [s_loc, heads, 128] }
+//     control words: arrived[2][world], done[2][world], two counters.
+
+#include "f2k_attn.h"
+
+#include "attn_launch.h"
+
+#include <cmath>
+#include <cstring>
+#include <new>
+#include <string>
+#include <vector>
+
+namespace {
+using namespace f2k;
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                   CUtensorMapFloatOOBfill);
+using WaitValue32Fn = CUresult (*)(CUstream, CUdeviceptr, cuuint32_t, unsigned int);
+
+void* driver_entry(const char* name) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint(name, &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+        return nullptr;
+    return p;
+}
+}  // namespace
+
+struct f2k_hx {
+    f2k_seqpar_config cfg{};
+    float  scale = 0.f;
+    bool   valid = false;
+    std::string err;
+    unsigned char* buf = nullptr;
+    size_t shard_bytes = 0, total_bytes = 0, flags_off = 0;
+    int    hpr = 0;                          // heads per rank
+    int*   d_status = nullptr;
+    std::vector<unsigned char*> peer;
+    unsigned int epoch = 0;
+    bool   exchanged = false, attended = false;
+    EncodeTiledFn encode = nullptr;
+    WaitValue32Fn wait32 = nullptr;
+    AttnParams params[2];                    // per buffer set; only the call number changes between steps
+    bool       have_params[2] = {false, false};
+
+    // set layout: Qh | Kh | Vh | O, each shard_bytes
+    unsigned char* part(unsigned char* base, int set, int which) const {
+        return base + ((size_t)set * 4 + which) * shard_bytes;
+    }
+    unsigned int* words(unsigned char* base) const { return reinterpret_cast<unsigned int*>(base + flags_off); }
+    unsigned int* arrived(unsigned char* base, int set, int src) const { return words(base) + set * 8 + src; }
+    unsigned int* done(unsigned char* base, int set, int src) const { return words(base) + 16 + set * 8 + src; }
+    unsigned int* counter(int i) const { return words(buf) + 32 + i; }
+};
+
+namespace {
+int fail(f2k_hx* h, int code, std::string msg) {
+    h->err = std::move(msg);
+    return code;
+}
+int fail_cuda(f2k_hx* h, const char* what, cudaError_t e) {
+    return fail(h, F2K_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
+}
+// [1, len, heads, 128] bf16 with the given token stride (elements)
+bool encode(f2k_hx* h, CUtensorMap* map, const void* base, int len, int heads, long long tok_stride) {
+    const cuuint64_t dims[4]    = {(cuuint64_t)kHeadDim, (cuuint64_t)heads, (cuuint64_t)len, 1};
+    const cuuint64_t strides[3] = {(cuuint64_t)kHeadDim * 2, (cuuint64_t)tok_stride * 2,
+                                   (cuuint64_t)tok_stride * (cuuint64_t)len * 2};
+    const cuuint32_t box[4]     = {64, 1, (cuuint32_t)kTileM, 1};
+    const cuuint32_t estr[4]    = {1, 1, 1, 1};
+    return h->encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+}  // namespace
+
+extern "C" {
+
+int f2k_hx_create(const f2k_seqpar_config* cfg, f2k_hx** out) {
+    if (!out) return F2K_ERR_INVALID;
+    *out = nullptr;
+    f2k_hx* h = new (std::nothrow) f2k_hx();
+    if (!h) return F2K_ERR_CUDA;
+    *out = h;
+    if (!cfg) return fail(h, F2K_ERR_INVALID, "null config");
+    h->cfg = *cfg;
+    if (cfg->batch != 1) return fail(h, F2K_ERR_UNSUPPORTED, "head exchange: batch must be 1");
+    if (cfg->seq_local <= 0 || cfg->n_heads <= 0 || cfg->head_dim <= 0)
+        return fail(h, F2K_ERR_INVALID, "head exchange: zero/negative dim");
+    if (cfg->world <= 0 || cfg->world > 8 || cfg->rank < 0 || cfg->rank >= cfg->world)
+        return fail(h, F2K_ERR_INVALID, "head exchange: world must be 1..8 and 0 <= rank < world");
+    if (cfg->n_heads % cfg->world != 0) return fail(h, F2K_ERR_INVALID, "head exchange: world must divide n_heads");
+    if (cfg->head_dim != kHeadDim) return fail(h, F2K_ERR_UNSUPPORTED, "head_dim must be 128");
+    h->hpr   = cfg->n_heads / cfg->world;
+    h->scale = cfg->scale > 0.f ? cfg->scale : 1.0f / std::sqrt((float)cfg->head_dim);
+    h->shard_bytes = (size_t)cfg->seq_local * cfg->n_heads * kHeadDim * 2;     // = world*s_loc*hpr*256
+    h->flags_off   = 8 * h->shard_bytes;
+    h->total_bytes = h->flags_off + 256;
+
+    int dev = 0, major = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail_cuda(h, "cudaGetDevice", e);
+    e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+    if (e != cudaSuccess) return fail_cuda(h, "cudaDeviceGetAttribute", e);
+    if (major != 10) return fail(h, F2K_ERR_UNSUPPORTED, "this library contains sm_100a code only");
+    h->encode = reinterpret_cast<EncodeTiledFn>(driver_entry("cuTensorMapEncodeTiled"));
+    h->wait32 = reinterpret_cast<WaitValue32Fn>(driver_entry("cuStreamWaitValue32"));
+    if (!h->encode || !h->wait32) return fail(h, F2K_ERR_CUDA, "driver entry points unavailable");
+    e = attn_fwd_prepare();
+    if (e == cudaSuccess) e = qk_prologue_prepare();
+    if (e != cudaSuccess) return fail_cuda(h, "kernel load", e);
+    e = cudaMalloc(reinterpret_cast<void**>(&h->buf), h->total_bytes);
+    if (e != cudaSuccess) return fail_cuda(h, "cudaMalloc(exchange buffer)", e);
+    e = cudaMemset(h->buf + h->flags_off, 0, 256);
+    if (e != cudaSuccess) return fail_cuda(h, "cudaMemset(flags)", e);
+    e = cudaMalloc(reinterpret_cast<void**>(&h->d_status), 256);
+    if (e == cudaSuccess) e = cudaMemset(h->d_status, 0, 256);
+    if (e != cudaSuccess) return fail_cuda(h, "cudaMalloc(status)", e);
+    h->peer.assign(cfg->world, nullptr);
+    h->peer[cfg->rank] = h->buf;
+    h->valid = true;
+    return F2K_OK;
+}
+
+void f2k_hx_destroy(f2k_hx* h) {
+    if (!h) return;
+    if (h->d_status) cudaFree(h->d_status);
+    if (h->buf) cudaFree(h->buf);
+    delete h;
+}
+
+const char* f2k_hx_last_error(const f2k_hx* h) { return h ? h->err.c_str() : "no handle"; }
+
+int f2k_hx_buffer(f2k_hx* h, void** base, size_t* bytes) {
+    if (!h || !h->valid) return F2K_ERR_INVALID;
+    if (base) *base = h->buf;
+    if (bytes) *bytes = h->total_bytes;
+    return F2K_OK;
+}
+
+int f2k_hx_attach(f2k_hx* h, void* const* peer_bases) {
+    if (!h || !h->valid || !peer_bases) return F2K_ERR_INVALID;
+    for (int r = 0; r < h->cfg.world; ++r) {
+        if (r == h->cfg.rank) continue;
+        if (!peer_bases[r]) return fail(h, F2K_ERR_INVALID, "null peer buffer");
+        h->peer[r] = static_cast<unsigned char*>(peer_bases[r]);
+    }
+    h->have_params[0] = h->have_params[1] = false;
+    return F2K_OK;
+}
+
+int f2k_hx_exchange_in(f2k_hx* h, const void* q_raw, const void* k_raw, const void* v, const void* gamma_q,
+                       const void* gamma_k, const float* cos_local, const float* sin_local, float eps,
+                       void* stream) {
+    if (!h || !h->valid) return F2K_ERR_INVALID;
+    if (!q_raw || !k_raw || !v || !gamma_q || !gamma_k || !cos_local || !sin_local)
+        return fail(h, F2K_ERR_INVALID, "null tensor pointer");
+    const f2k_seqpar_config& c = h->cfg;
+    for (int r = 0; r < c.world; ++r)
+        if (!h->peer[r]) return fail(h, F2K_ERR_INVALID, "peers not attached");
+    h->epoch += 1;
+    const int set = h->epoch & 1;
+    QkvScatterParams p;
+    std::memset(&p, 0, sizeof p);
+    p.q = q_raw; p.k = k_raw; p.v = v;
+    p.gamma_q = gamma_q; p.gamma_k = gamma_k;
+    p.cos_tab = cos_local; p.sin_tab = sin_local;
+    for (int r = 0; r < c.world; ++r) {
+        p.dst_q[r] = h->part(h->peer[r], set, 0);
+        p.dst_k[r] = h->part(h->peer[r], set, 1);
+        p.dst_v[r] = h->part(h->peer[r], set, 2);
+        p.flag[r]  = h->arrived(h->peer[r], set, c.rank);
+    }
+    p.counter = h->counter(0);
+    p.value   = h->epoch;
+    p.s_loc = c.seq_local; p.n_heads = c.n_heads; p.heads_per_rank = h->hpr; p.world = c.world; p.rank = c.rank;
+    p.eps = eps;
+    const cudaError_t e = qkv_scatter_launch(p, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail_cuda(h, "exchange kernel launch", e);
+    h->exchanged = true;
+    return F2K_OK;
+}
+
+int f2k_hx_attend(f2k_hx* h, void* stream) {
+    if (!h || !h->valid) return F2K_ERR_INVALID;
+    if (!h->exchanged) return fail(h, F2K_ERR_INVALID, "attend without exchange_in");
+    const f2k_seqpar_config& c = h->cfg;
+    const int set = h->epoch & 1;
+    AttnParams& p = h->params[set];
+    if (!h->have_params[set]) {
+        std::memset(&p, 0, sizeof p);
+        const long long tok_h = (long long)h->hpr * kHeadDim;          // token stride of the head-sharded tensors
+        const long long tok_o = (long long)c.n_heads * kHeadDim;       // token stride of the token-sharded output
+        const int tiles_per_seg = (c.seq_local + kTileM - 1) / kTileM;
+        const size_t seg_bytes = (size_t)c.seq_local * h->hpr * kHeadDim * 2;
+        for (int s = 0; s < c.world; ++s) {                            // segment s = the tokens of rank s
+            if (!encode(h, &p.tm_q[s], h->part(h->buf, set, 0) + s * seg_bytes, c.seq_local, h->hpr, tok_h) ||
+                !encode(h, &p.tm_k[s], h->part(h->buf, set, 1) + s * seg_bytes, c.seq_local, h->hpr, tok_h) ||
+                !encode(h, &p.tm_v[s], h->part(h->buf, set, 2) + s * seg_bytes, c.seq_local, h->hpr, tok_h))
+                return fail(h, F2K_ERR_CUDA, "tensor map failed");
+            // the output rows of segment s go to rank s, into the columns of this rank's heads
+            p.o_ptr[s] = h->part(h->peer[s], set, 3) + (size_t)c.rank * h->hpr * kHeadDim * 2;
+            p.o_tok_stride[s]   = tok_o;
+            p.o_batch_stride[s] = tok_o * c.seq_local;
+            p.q_len[s] = p.kv_len[s] = c.seq_local;
+            p.q_tile_start[s] = p.kv_tile_start[s] = s * tiles_per_seg;
+            if (s != c.rank) p.q_ready[s] = p.kv_ready[s] = h->arrived(h->buf, set, s);
+            p.done_flag[s] = h->done(h->peer[s], set, c.rank);
+        }
+        // this rank's own rows come from the kernel just before on the same stream: no wait needed
+        p.q_tile_start[c.world] = p.kv_tile_start[c.world] = c.world * tiles_per_seg;
+        p.n_qseg = p.n_kvseg = c.world;
+        p.n_q_tiles = p.n_kv_tiles = c.world * tiles_per_seg;
+        p.kv_ready_heads_per_group = h->hpr;                            // one word per source rank
+        p.n_heads = h->hpr;
+        p.batch = 1;
+        p.scale_log2 = h->scale * 1.4426950408889634f;
+        p.status = h->d_status;
+        p.done_counter = h->counter(1);
+        p.n_done = c.world;
+        h->have_params[set] = true;
+    }
+    p.kv_ready_value = h->epoch;
+    p.done_value = h->epoch;
+    const cudaError_t e = attn_fwd_launch(p, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail_cuda(h, "attention launch", e);
+    h->exchanged = false;
+    h->attended = true;
+    return F2K_OK;
+}
+
+int f2k_hx_output(f2k_hx* h, void** o_local, void* stream) {
+    if (!h || !h->valid) return F2K_ERR_INVALID;
+    if (!h->attended) return fail(h, F2K_ERR_INVALID, "output without attend");
+    const int set = h->epoch & 1;
+    for (int s = 0; s < h->cfg.world; ++s)
+        if (h->wait32(static_cast<CUstream>(stream), reinterpret_cast<CUdeviceptr>(h->done(h->buf, set, s)), h->epoch,
+                      0 /* CU_STREAM_WAIT_VALUE_GEQ */) != CUDA_SUCCESS)
+            return fail(h, F2K_ERR_CUDA, "cuStreamWaitValue32 failed");
+    if (o_local) *o_local = h->part(h->buf, set, 3);
+    return F2K_OK;
+}
+
+int f2k_hx_device_status(f2k_hx* h, int* status_out) {
+    if (!h || !h->valid) return F2K_ERR_INVALID;
+    int st = 0;
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return fail_cuda(h, "cudaDeviceSynchronize", e);
+    e = cudaMemcpy(&st, h->d_status, sizeof st, cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return fail_cuda(h, "status read", e);
+    if (st != 0) cudaMemset(h->d_status, 0, sizeof st);
+    if (status_out) *status_out = st;
+    if (st != 0) return fail(h, F2K_ERR_DEVICE, "a bounded wait inside the attention kernel expired");
+    return F2K_OK;
+}
+
+}  // extern "C"

@@ -85,16 +85,17 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
     }
 }
 
-// Bounded wait on a word in global memory that another engine of this GPU (a copy engine, a
-// stream memory operation) sets to `value`. Same contract as mbar_wait.
+// Bounded wait on a word in global memory that someone else - a copy engine, a stream memory
+// operation, a kernel on another GPU - sets to `value` (or to the value of a later call: the
+// comparison is "not before", modulo 2^32). Same contract as mbar_wait.
 __device__ __forceinline__ bool global_flag_wait(const unsigned int* flag, unsigned int value,
                                                  volatile uint32_t* abort_flag,
                                                  long long limit_cycles = 2000000000ll) {
     long long t0 = 0;
     for (uint32_t spins = 1;; ++spins) {
         unsigned int v;
-        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
-        if (v == value) return true;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+        if ((int)(v - value) >= 0) return true;
         if ((spins & 63u) == 0u) {
             if (*abort_flag != 0u) return false;
             const long long now = clock64();
@@ -106,6 +107,26 @@ __device__ __forceinline__ bool global_flag_wait(const unsigned int* flag, unsig
             }
         }
         __nanosleep(200);
+    }
+}
+
+// Store with release semantics at system scope: everything this thread has observed or written
+// (and fenced) before it is visible to whoever acquires the word, on this GPU or another.
+__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Called by one thread of every CTA after a CTA-wide barrier that follows the CTA's last global
+// store: the last CTA of the grid to arrive publishes `value` to the `n` words. The counter
+// (zero before the launch) is zero again afterwards.
+__device__ __forceinline__ void grid_done_publish(unsigned int* counter, unsigned int n_ctas,
+                                                  unsigned int* const* flags, int n, unsigned int value) {
+    __threadfence_system();
+    const unsigned int seen = atomicAdd(counter, 1u);
+    if (seen == n_ctas - 1u) {
+        atomicExch(counter, 0u);
+        __threadfence_system();
+        for (int i = 0; i < n; ++i) st_release_sys(flags[i], value);
     }
 }
 

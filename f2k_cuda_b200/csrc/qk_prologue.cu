@@ -136,6 +136,79 @@ qk_prologue_kernel(const __grid_constant__ QkPrologueParams p) {
 }
 
 // ---------------------------------------------------------------------------------
+// Head exchange: the same row arithmetic, every row stored into the memory of the rank that owns
+// its head (peer stores over NVLink, 256 contiguous bytes per half-warp and row). Work item =
+// kGroup consecutive heads (all of one destination) of one token of one of the three tensors.
+// ---------------------------------------------------------------------------------
+template <int kGroup>
+__global__ void __launch_bounds__(kBlock, 4)
+qkv_scatter_kernel(const __grid_constant__ QkvScatterParams p) {
+    const int hl = threadIdx.x & 15;
+    const long long per_tensor = (long long)p.s_loc * p.n_heads / kGroup;
+    const long long total = 3 * per_tensor;
+    const long long n_hw  = (long long)gridDim.x * (kBlock / 16);
+    for (long long grp = (long long)blockIdx.x * (kBlock / 16) + (threadIdx.x >> 4); grp < total; grp += n_hw) {
+        const int which = (int)(grp / per_tensor);                       // 0 q, 1 k, 2 v
+        const long long lr = (grp - which * per_tensor) * kGroup;        // row inside the tensor
+        const int tok = (int)(lr / p.n_heads);
+        const int hd0 = (int)(lr - (long long)tok * p.n_heads);
+        const int dst_rank = hd0 / p.heads_per_rank;
+        const int hh = hd0 - dst_rank * p.heads_per_rank;
+        const void* xin = which == 0 ? p.q : (which == 1 ? p.k : p.v);
+        unsigned char* base = which == 0 ? p.dst_q[dst_rank] : (which == 1 ? p.dst_k[dst_rank] : p.dst_v[dst_rank]);
+        const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(xin) + lr * kHeadDim);
+        uint4* dst = reinterpret_cast<uint4*>(
+            base + (((long long)p.rank * p.s_loc + tok) * p.heads_per_rank + hh) * (long long)(kHeadDim * 2));
+        uint4 raw[kGroup];
+#pragma unroll
+        for (int u = 0; u < kGroup; ++u) raw[u] = src[u * 16 + hl];
+        if (which == 2) {
+#pragma unroll
+            for (int u = 0; u < kGroup; ++u) dst[u * 16 + hl] = raw[u];
+            continue;
+        }
+        const uint4  graw = __ldg(reinterpret_cast<const uint4*>(which == 0 ? p.gamma_q : p.gamma_k) + hl);
+        const float4 c4 = __ldg(reinterpret_cast<const float4*>(p.cos_tab + (long long)tok * 64) + hl);
+        const float4 s4 = __ldg(reinterpret_cast<const float4*>(p.sin_tab + (long long)tok * 64) + hl);
+        float g[8];
+        unpack8(graw, g);
+        const float cs[4] = {c4.x, c4.y, c4.z, c4.w};
+        const float sn[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+        for (int u = 0; u < kGroup; ++u) {
+            float v[8];
+            unpack8(raw[u], v);
+            float ss = 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ss = fmaf(v[i], v[i], ss);
+            ss = half_warp_sum(ss);
+            const float rrms = rsqrtf(ss * (1.0f / kHeadDim) + p.eps);
+            float y[8];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float a = v[2 * k] * rrms * g[2 * k];
+                const float b = v[2 * k + 1] * rrms * g[2 * k + 1];
+                rotate_pair(y[2 * k], y[2 * k + 1], a, b, cs[k], sn[k]);
+            }
+            dst[u * 16 + hl] = pack8(y);
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        // the same publication as f2k::ptx::grid_done_publish, spelled out here to keep this file
+        // free of the PTX header
+        __threadfence_system();
+        const unsigned int seen = atomicAdd(p.counter, 1u);
+        if (seen == gridDim.x - 1u) {
+            atomicExch(p.counter, 0u);
+            __threadfence_system();
+            for (int i = 0; i < p.world; ++i)
+                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.flag[i]), "r"(p.value) : "memory");
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------
 // Stand-alone RMSNorm. dim == 128: half-warp per row, one pass. Other dims (multiple
 // of 8): one warp per row, two passes over the row (the second hits L1/L2).
 // y = bf16( x * rsqrt(mean(x^2) + eps) * gamma ), fp32 arithmetic.
@@ -268,6 +341,8 @@ cudaError_t qk_prologue_prepare() {
     cudaFuncAttributes attr;
     cudaError_t e = cudaFuncGetAttributes(&attr, qk_prologue_kernel<4>);
     if (e == cudaSuccess) e = cudaFuncGetAttributes(&attr, qk_prologue_kernel<1>);
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&attr, qkv_scatter_kernel<4>);
+    if (e == cudaSuccess) e = cudaFuncGetAttributes(&attr, qkv_scatter_kernel<1>);
     return e;
 }
 
@@ -281,6 +356,16 @@ cudaError_t qk_prologue_launch(const QkPrologueParams& params, cudaStream_t stre
         qk_prologue_kernel<4><<<grid_for(total / 4, kBlock / 16), kBlock, 0, stream>>>(p);
     else
         qk_prologue_kernel<1><<<grid_for(total, kBlock / 16), kBlock, 0, stream>>>(p);
+    return cudaPeekAtLastError();
+}
+
+cudaError_t qkv_scatter_launch(const QkvScatterParams& p, cudaStream_t stream) {
+    const long long rows = 3ll * p.s_loc * p.n_heads;
+    if (rows <= 0) return cudaErrorInvalidValue;
+    if (p.heads_per_rank % 4 == 0)
+        qkv_scatter_kernel<4><<<grid_for(rows / 4, kBlock / 16), kBlock, 0, stream>>>(p);
+    else
+        qkv_scatter_kernel<1><<<grid_for(rows, kBlock / 16), kBlock, 0, stream>>>(p);
     return cudaPeekAtLastError();
 }
 

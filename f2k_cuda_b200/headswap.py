@@ -1,0 +1,98 @@
+"""Sequence-parallel attention by head exchange (host side).
+
+One process per GPU. Rank r holds the raw Q, K, V of its `seq_local` tokens (all heads) and gets
+the attention output of those tokens; inside, every rank attends n_heads / world heads over all
+tokens. The exchange is done by the kernels themselves with stores into peer memory (see
+csrc/headswap.cu). torch.distributed is used once, to hand the IPC handles around.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+from . import _lib
+from ._lib import SeqParConfig, lib
+from .seqpar import _tensor_from_ptr
+
+
+class HeadExchangeAttention:
+    def __init__(self, seq_local: int, n_heads: int, head_dim: int, world: int, rank: int, scale: float = 0.0):
+        self.world, self.rank = world, rank
+        self.seq_local, self.n_heads, self.head_dim = seq_local, n_heads, head_dim
+        self._h = C.c_void_p()
+        cfg = SeqParConfig(1, seq_local, n_heads, head_dim, world, rank, scale)
+        self._rc = lib.f2k_hx_create(C.byref(cfg), C.byref(self._h))
+        self._opened = []
+
+    def __del__(self):
+        if lib is None:          # interpreter shutdown
+            return
+        for base in getattr(self, "_opened", []):
+            lib.f2k_ipc_close(base)
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            lib.f2k_hx_destroy(h)
+
+    def ok(self) -> bool:
+        return self._rc == _lib.F2K_OK
+
+    def last_error(self) -> str:
+        return lib.f2k_hx_last_error(self._h).decode() if self._h else "no handle"
+
+    def buffer(self):
+        base, n = C.c_void_p(), C.c_size_t()
+        lib.f2k_hx_buffer(self._h, C.byref(base), C.byref(n))
+        return base.value, n.value
+
+    def attach_in_process(self, ranks) -> bool:
+        """All ranks live in this process on one GPU (tests): attach their buffers by pointer."""
+        bases = (C.c_void_p * self.world)(*[r.buffer()[0] for r in ranks])
+        return lib.f2k_hx_attach(self._h, bases) == _lib.F2K_OK
+
+    def attach_distributed(self, group=None) -> bool:
+        """Exchange IPC handles over torch.distributed (any backend) and map every peer's buffer."""
+        import torch.distributed as dist
+        handle = (C.c_ubyte * 64)()
+        if lib.f2k_ipc_export(C.c_void_p(self.buffer()[0]), handle) != _lib.F2K_OK:
+            return False
+        handles = [None] * self.world
+        dist.all_gather_object(handles, bytes(handle), group=group)
+        bases = (C.c_void_p * self.world)()
+        for r, hb in enumerate(handles):
+            if r == self.rank:
+                bases[r] = self.buffer()[0]
+                continue
+            base = C.c_void_p()
+            if lib.f2k_ipc_open((C.c_ubyte * 64).from_buffer_copy(hb), C.byref(base)) != _lib.F2K_OK:
+                return False
+            self._opened.append(base)
+            bases[r] = base.value
+        return lib.f2k_hx_attach(self._h, bases) == _lib.F2K_OK
+
+    # ---- per step, all on one stream ------------------------------------------------------
+    @staticmethod
+    def _stream(stream):
+        import torch
+        return C.c_void_p((stream or torch.cuda.current_stream()).cuda_stream)
+
+    def exchange_in(self, q_raw, k_raw, v, gamma_q, gamma_k, cos_local, sin_local, eps: float, stream=None) -> bool:
+        """q_raw, k_raw, v: [1, seq_local, n_heads, 128] bf16; cos_local/sin_local: this rank's rows
+        of the RoPE tables. Normalises + rotates Q and K and sends every head to its rank."""
+        p = lambda t: C.c_void_p(t.data_ptr())  # noqa: E731
+        return lib.f2k_hx_exchange_in(self._h, p(q_raw), p(k_raw), p(v), p(gamma_q), p(gamma_k), p(cos_local),
+                                      p(sin_local), eps, self._stream(stream)) == _lib.F2K_OK
+
+    def attend(self, stream=None) -> bool:
+        return lib.f2k_hx_attend(self._h, self._stream(stream)) == _lib.F2K_OK
+
+    def output(self, stream=None):
+        """Makes the stream wait for every rank's contribution; returns this rank's
+        [1, seq_local, n_heads, 128] output (a view into the exchange buffer)."""
+        o = C.c_void_p()
+        if lib.f2k_hx_output(self._h, C.byref(o), self._stream(stream)) != _lib.F2K_OK:
+            return None
+        return _tensor_from_ptr(o.value, (1, self.seq_local, self.n_heads, self.head_dim))
+
+    def device_status(self) -> int:
+        st = C.c_int(0)
+        lib.f2k_hx_device_status(self._h, C.byref(st))
+        return st.value

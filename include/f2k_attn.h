@@ -243,6 +243,34 @@ int f2k_seqpar_forward(f2k_seqpar* h, const void* q_local, void* o_local, int ov
                        void* compute_stream, void* copy_stream);
 int f2k_seqpar_device_status(f2k_seqpar* h, int* status_out);
 
+/* ---- sequence-parallel attention by head exchange ----------------------------------------
+ * Same sharding outside (rank r holds Q, K, V of its seq_local tokens, all heads, and gets the
+ * output of its tokens), but inside the attention the HEADS are sharded: every rank attends
+ * n_heads / world heads over all tokens. The exchange is done by the kernels themselves with
+ * stores into peer memory: one kernel normalises + rotates Q and K and scatters Q, K, V by head
+ * (exchange_in); the attention kernel's epilogue writes every output row into the buffer of the
+ * rank that owns the token (attend). Traffic per GPU and step is 4 * (world-1)/world shards
+ * against 2 * (world-1) shards for the ring above. batch must be 1; world must divide n_heads.
+ * Uses f2k_seqpar_config; buffers are exported/attached like the ring's. No reference
+ * counterpart. Call order per step, all on one stream: exchange_in, attend, output. */
+typedef struct f2k_hx f2k_hx; /* opaque */
+int         f2k_hx_create(const f2k_seqpar_config* cfg, f2k_hx** out);
+void        f2k_hx_destroy(f2k_hx* h);
+const char* f2k_hx_last_error(const f2k_hx* h);
+int f2k_hx_buffer(f2k_hx* h, void** base, size_t* bytes);
+int f2k_hx_attach(f2k_hx* h, void* const* peer_bases);
+/* q_raw, k_raw, v: this rank's [seq_local, n_heads, 128] bf16 (raw projections); gains [128] bf16;
+ * cos_local/sin_local: this rank's rows of the RoPE tables, [seq_local, 64] fp32. */
+int f2k_hx_exchange_in(f2k_hx* h, const void* q_raw, const void* k_raw, const void* v,
+                       const void* gamma_q, const void* gamma_k,
+                       const float* cos_local, const float* sin_local, float eps, void* stream);
+int f2k_hx_attend(f2k_hx* h, void* stream);
+/* Makes `stream` wait until every rank has written its heads of this rank's rows; *o_local is
+ * then this rank's [seq_local, n_heads, 128] bf16 output (inside the exchange buffer; valid
+ * until the exchange_in after next). */
+int f2k_hx_output(f2k_hx* h, void** o_local, void* stream);
+int f2k_hx_device_status(f2k_hx* h, int* status_out);
+
 /* CUDA IPC for the shard buffers: 64-byte handles to pass between the rank processes. */
 int f2k_ipc_export(const void* base, void* handle64);
 int f2k_ipc_open(const void* handle64, void** base);
