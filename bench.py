@@ -45,7 +45,7 @@ UNIT = "TFLOP/s"
 FALLBACK_PEAK_TFLOPS = 1590.0
 # DRAM bytes (read + write) of one attention-kernel launch at S=4608, B=1, H=32: dram__bytes_read.sum
 # + dram__bytes_write.sum of the ncu capture summarised in profiles/attn_fwd_sm100_s4608.md.
-ATTN_DRAM_TRAFFIC_BYTES = 132.6e6
+ATTN_DRAM_TRAFFIC_BYTES = 129.9e6
 
 
 def parse_args():
