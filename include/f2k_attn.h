@@ -18,6 +18,10 @@
  *    one host thread at a time. Distinct handles on distinct streams are independent.
  *  - There is no CPU fallback and no other GPU path: on a device that is not
  *    compute capability 10.x, or for head_dim != 128, creation fails with a message.
+ *  - Three environment variables override choices the library otherwise makes itself; they
+ *    exist for measurements and tests: F2K_HOST_PIPELINE = "rows" | "heads" and
+ *    F2K_HOST_GROUPS = n (how f2k_attn_forward_fused_host splits its work),
+ *    F2K_SEQPAR_GROUPS = n (head groups a shard is pulled in by f2k_seqpar_forward).
  */
 #ifndef F2K_ATTN_H
 #define F2K_ATTN_H
