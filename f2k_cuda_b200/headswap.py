@@ -14,6 +14,24 @@ from ._lib import SeqParConfig, lib
 from .seqpar import _tensor_from_ptr
 
 
+def head_exchange_plan(seq_local: int, n_heads: int, world: int, rank: int) -> dict:
+    """Where `rank`'s rows go, as the kernels compute it (pure host logic, tested on CPU).
+
+    Inbound: head h of local token t is stored on rank h // heads_per_rank, in that rank's
+    [world * seq_local, heads_per_rank, 128] buffers, at token rank * seq_local + t, head
+    h % heads_per_rank. Outbound: the attention output of query segment s (the tokens of rank s)
+    is stored on rank s, in its [seq_local, n_heads, 128] buffer, in head columns
+    [rank * heads_per_rank, (rank + 1) * heads_per_rank)."""
+    if world <= 0 or n_heads % world != 0 or not 0 <= rank < world:
+        raise ValueError("world must divide n_heads and 0 <= rank < world")
+    hpr = n_heads // world
+    return {
+        "heads_per_rank": hpr,
+        "send": [{"to": d, "heads": (d * hpr, (d + 1) * hpr), "token_offset": rank * seq_local} for d in range(world)],
+        "return": [{"to": s, "tokens_of_rank": s, "head_columns": (rank * hpr, (rank + 1) * hpr)} for s in range(world)],
+    }
+
+
 class HeadExchangeAttention:
     def __init__(self, seq_local: int, n_heads: int, head_dim: int, world: int, rank: int, scale: float = 0.0):
         self.world, self.rank = world, rank

@@ -111,7 +111,7 @@ def _gloo_worker(rank, world, port, seq, out):
         dist.all_gather_object(got, handle)
         plans = [None] * world
         dist.all_gather_object(plans, (plan_ring(world, rank), shard_bounds(seq, world, rank)))
-        # the per-step "K/V written" barrier is one tiny all-reduce
+        # the benchmark's only collective: a tiny all-reduce of the measured time (a step has none)
         import torch
         t = torch.ones(1)
         dist.all_reduce(t)
@@ -149,3 +149,78 @@ def test_bench_rank_problem_shards_heads_not_work():
     for n in (1, 2, 4, 8):
         w = Workload("s4608", n, 512, ((64, 64),), n_heads=32 // n)
         assert w.batch * w.n_heads == 32
+
+
+def _head_exchange_worker(rank, world, port, out):
+    """One rank of the head exchange with numpy standing in for the kernels: scatter the rank's
+    normalised rows by head (an object all-gather stands in for the peer stores), attend the
+    rank's heads over all tokens, send every output row back to the rank that owns the token."""
+    import torch.distributed as dist
+    import oracle
+    from f2k_cuda_b200.headswap import head_exchange_plan
+    from tests._util import normal_bits
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        orc = oracle.load_oracle()
+        per, H, D = 48, 4, 128
+        S = world * per
+        q, k, v = (normal_bits(0x4EAD, i, (1, S, H, D)) for i in range(3))      # every rank draws the whole problem
+        plan = head_exchange_plan(per, H, world, rank)
+        hpr = plan["heads_per_rank"]
+        mine = slice(rank * per, (rank + 1) * per)
+        # inbound: what this rank would store into each destination's buffers
+        parcels = {}
+        for dst in plan["send"]:
+            h0, h1 = dst["heads"]
+            parcels[dst["to"]] = (dst["token_offset"], q[:, mine, h0:h1], k[:, mine, h0:h1], v[:, mine, h0:h1])
+        everyone = [None] * world
+        dist.all_gather_object(everyone, parcels)
+        qh = np.zeros((1, S, hpr, D), np.uint16); kh = np.zeros_like(qh); vh = np.zeros_like(qh)
+        for src in range(world):
+            off, pq, pk, pv = everyone[src][rank]
+            qh[:, off:off + per], kh[:, off:off + per], vh[:, off:off + per] = pq, pk, pv
+        _, oh = orc.joint_path(q_img=qh, k_img=kh, v_img=vh)                  # this rank's heads, all tokens
+        # outbound: rows of segment s go to rank s, into this rank's head columns
+        back = {r["to"]: (r["head_columns"], oh[:, r["tokens_of_rank"] * per:(r["tokens_of_rank"] + 1) * per])
+                for r in plan["return"]}
+        everyone = [None] * world
+        dist.all_gather_object(everyone, back)
+        o = np.zeros((1, per, H, D), np.float32)
+        for src in range(world):
+            (c0, c1), rows = everyone[src][rank]
+            o[:, :, c0:c1] = rows
+        _, full = orc.joint_path(q_img=q, k_img=k, v_img=v)
+        out[rank] = float(np.max(np.abs(o - full[:, mine])))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_head_exchange_with_two_gloo_ranks():
+    import torch.multiprocessing as mp
+    world = 2
+    mgr = mp.Manager()
+    out = mgr.dict()
+    port = _free_port()
+    ctx = mp.get_context("spawn")
+    procs = [ctx.Process(target=_head_exchange_worker, args=(r, world, port, out)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(180)
+        assert p.exitcode == 0
+    assert all(out[r] == 0.0 for r in range(world)), dict(out)   # same arithmetic per head: identical
+
+
+def test_head_exchange_plan_covers_every_head_once():
+    from f2k_cuda_b200.headswap import head_exchange_plan
+    for world in (1, 2, 4, 8):
+        seen = []
+        for rank in range(world):
+            plan = head_exchange_plan(2112, 32, world, rank)
+            assert [d["heads"] for d in plan["send"]] == [(d * 32 // world, (d + 1) * 32 // world) for d in range(world)]
+            assert all(d["token_offset"] == rank * 2112 for d in plan["send"])
+            seen += [r["head_columns"] for r in plan["return"] if r["to"] == 0]
+        assert sorted(seen) == [(r * 32 // world, (r + 1) * 32 // world) for r in range(world)]
+    with pytest.raises(ValueError):
+        head_exchange_plan(128, 6, 4, 0)
