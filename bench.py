@@ -40,11 +40,13 @@ if str(ROOT) not in sys.path:
 import numpy as np  # noqa: E402
 import torch  # noqa: E402
 
+HEADLINE_WORKLOAD = "s4608 joint attention (512 text + 64x64 image tokens, hd128), batch 1, 32 heads"
 METRIC = "joint_attn_tflops"
 UNIT = "TFLOP/s"
 FALLBACK_PEAK_TFLOPS = 1590.0
-# DRAM bytes (read + write) of one attention-kernel launch at S=4608, B=1, H=32: dram__bytes_read.sum
-# + dram__bytes_write.sum of the ncu capture summarised in profiles/attn_fwd_sm100_s4608.md.
+STRONG_SECTION_LIMIT_S = 420
+# DRAM bytes (read + write) of one attention-kernel launch at S=4608, B=1, H=32, as counted by one
+# ncu capture (dram__bytes_read.sum + dram__bytes_write.sum); algorithmic minimum 151.0 MB.
 ATTN_DRAM_TRAFFIC_BYTES = 129.9e6
 
 
@@ -66,20 +68,27 @@ def parse_args():
     ap.add_argument("--no-reference-kernel", action="store_true",
                     help="skip the short leg that times the reference's rebuilt kernels beside ours (N = 1)")
     ap.add_argument("--skip-denoise-step", action="store_true", help="skip the 32-call CUDA-graph leg (N = 1)")
+    ap.add_argument("--skip-sustained", action="store_true", help="skip the seconds-long back-to-back leg (N = 1)")
+    ap.add_argument("--sustained-seconds", type=float, default=2.5)
+    ap.add_argument("--skip-strong-scaling", action="store_true",
+                    help="N > 1: skip the fixed jobs (heads / sequence / head exchange) after the headline legs")
     ap.add_argument("--skip-e2e", action="store_true",
                     help="skip the host-buffer leg (for short profiler captures; the line then has e2e null)")
     return ap.parse_args()
 
 
-def measured_peak():
+def measured_peak(key="bf16_tflops"):
     f = ROOT / "MEASURED_PEAKS.json"
     if f.exists():
         try:
             d = json.loads(f.read_text())
-            return float(d["bf16_tflops"]), "measured bf16_tflops (cuBLAS burst, MEASURED_PEAKS.json)"
+            what = "cuBLAS burst" if key == "bf16_tflops" else "cuBLAS back to back for seconds"
+            return float(d[key]), f"measured {key} ({what}, MEASURED_PEAKS.json)"
         except Exception:
             pass
-    return FALLBACK_PEAK_TFLOPS, "fallback 1590 TFLOP/s (MEASURED_PEAKS.json absent)"
+    if key == "bf16_tflops":
+        return FALLBACK_PEAK_TFLOPS, "fallback 1590 TFLOP/s (MEASURED_PEAKS.json absent)"
+    return 1400.0, "fallback 1400 TFLOP/s sustained (MEASURED_PEAKS.json absent)"
 
 
 class ClockSampler:
@@ -131,6 +140,16 @@ class ClockSampler:
         load = [x for x in self.samples if x >= 0.6 * top]       # samples taken while kernels ran
         return {"sm_mhz": statistics.median(load), "sm_min_mhz": min(load), "sm_max_mhz": self.max_mhz,
                 "reasons": sorted(n for bit, n in self.REASONS.items() if self.mask & bit), "samples": len(self.samples)}
+
+    def bins(self, width_mhz: int = 100):
+        """Share of the samples per SM-clock bin (lower edge in MHz)."""
+        if not self.samples:
+            return {}
+        out = {}
+        for x in self.samples:
+            k = str(int(x // width_mhz) * width_mhz)
+            out[k] = out.get(k, 0) + 1
+        return {k: round(v / len(self.samples), 3) for k, v in sorted(out.items(), key=lambda kv: int(kv[0]))}
 
 
 def dev_bf16(bits):
@@ -196,46 +215,66 @@ def cpu_baseline(problem, tabs, flops_per_head):
             "sample": f"batch element 0, heads 0..{n - 1} of {H} (S=4608): QK-norm + RoPE + fp32 attention, {t:.1f} s"}
 
 
-def denoise_step_leg(f2k, d, dg, dtab, o_t, o_i, ws, ja, B, St, Si, H, D, stream, flops_per_call):
-    """The 32 attention calls of one denoise step (reference: 8 DoubleStreamBlock + 24
-    SingleStreamBlock forwards), captured once as a CUDA graph and replayed: time per step and per
-    call without per-call launch overhead. Single-stream blocks see one combined stream."""
-    S = St + Si
-    single = f2k.Attention(f2k.Attention.Config(B, S, H, D))
-    if not single.ok():
-        return {"unavailable": single.last_error()}
+def denoise_step_leg(d, dg, dtab, o_t, o_i, B, St, Si, H, D, stream, flops_per_call, guidance):
+    """The attention calls of one denoise step (reference: 8 DoubleStreamBlock + 24 SingleStreamBlock
+    forwards per model forward, flux_transformer.cu:412-439; two model forwards per step under
+    classifier-free guidance, tools/serve.cu:563-566), captured once as a CUDA graph and replayed:
+    time per step and per call without per-call launch overhead. Every call of a kind reads the same
+    input tensors (memory), which does not change its work."""
+    from f2k_cuda_b200.step import DoubleCall, SingleCall, StepAttention
+    step = StepAttention(B, St, Si, H, D)
+    if not step.ok():
+        return {"unavailable": step.last_error()}
     qc, kc, vc = (torch.cat([d[i], d[i + 3]], 1).contiguous() for i in range(3))
     oc = torch.empty_like(qc)
     tab_c = [torch.cat([dtab[0], dtab[2]]).contiguous(), torch.cat([dtab[1], dtab[3]]).contiguous()]
-    ws_c = torch.empty(single.fused_workspace_size_bytes(), dtype=torch.uint8, device="cuda")
-    g_single = [None, None, dg[2], dg[3]]
-    t_single = [None, None, tab_c[0], tab_c[1]]
-
-    def one_step():
-        for _ in range(8):
-            if not ja.forward_fused(*d, dg, dtab, 1e-6, o_t, o_i, ws):
-                raise RuntimeError(ja.last_error())
-        for _ in range(24):
-            if not single.forward_fused(None, None, None, qc, kc, vc, g_single, t_single, 1e-6, None, oc, ws_c):
-                raise RuntimeError(single.last_error())
-
-    one_step()                                     # tensor maps built, kernels loaded
-    torch.cuda.synchronize()
-    side = torch.cuda.Stream()
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.stream(side):
-        with torch.cuda.graph(graph, stream=side):
-            one_step()
-    torch.cuda.synchronize()
+    one_pass = ([DoubleCall(*d, o_t, o_i)] * 8, [SingleCall(qc, kc, vc, oc)] * 24)
+    passes = [one_pass] * (2 if guidance else 1)
+    graph, calls = step.capture(passes, dg, dtab, tab_c)
     for _ in range(2):
         graph.replay()
     reps = 5
     ms = time_region(graph.replay, reps, stream)
-    if ja.device_status() != 0 or single.device_status() != 0:
+    if step.device_status() != 0:
         raise RuntimeError("attention kernel reported a device-side error in the denoise-step leg")
-    return {"calls": 32, "ms_per_step": ms, "ms_per_call": ms / 32, "value": 32 * flops_per_call / (ms * 1e-3) / 1e12,
-            "unit": UNIT, "launch": "one CUDA graph of 64 kernels, replayed", "steps": reps,
-            "what": "8 joint calls (512 + 4096 tokens) + 24 single-stream calls (4608 tokens), fused prologue each"}
+    return {"calls": calls, "ms_per_step": ms, "ms_per_call": ms / calls,
+            "value": calls * flops_per_call / (ms * 1e-3) / 1e12, "unit": UNIT,
+            "launch": f"one CUDA graph of {2 * calls} kernels, replayed", "steps": reps,
+            "what": ("classifier-free guidance, two model forwards: 2 x " if guidance else "") +
+                    "(8 joint calls (512 + 4096 tokens) + 24 single-stream calls (4608 tokens)), fused prologue each"}
+
+
+def _headline_line(args, world, flops, ms, ms_attn, ms_e2e, e2e_steps, d, o_t, o_i, clocks, B, H, St, Si, D):
+    peak, peak_src = measured_peak()
+    achieved = flops / (ms_attn * 1e-3) / 1e12
+    in_bytes = sum(x.numel() * 2 for x in d)
+    out_bytes = o_t.numel() * 2 + o_i.numel() * 2
+    line = {
+        "metric": METRIC, "value": world * flops / (ms * 1e-3) / 1e12, "unit": UNIT,
+        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": HEADLINE_WORKLOAD if world == 1 else
+                               "s4608 joint attention (512 text + 64x64 image tokens, hd128), "
+                               f"batch {B}, {H} heads per GPU (heads sharded)",
+                   "step": "fused QK-RMSNorm + 4-axis RoPE + non-causal attention, one call",
+                   "flops_per_step_per_gpu": flops, "seq": St + Si, "head_dim": D,
+                   "l2": "inputs + outputs + workspace of a step exceed the 126 MB L2 (226 MB)",
+                   "parallelism": f"heads{world}" if world > 1 else "single"},
+        "per_gpu_tflops": flops / (ms * 1e-3) / 1e12,
+        "pct_of_peak": 100.0 * flops / (ms * 1e-3) / 1e12 / peak,
+        "roofline": {"bound": "tensor", "kernel": "attn_fwd_sm100_kernel", "achieved": achieved, "peak": peak,
+                     "unit": UNIT, "frac": achieved / peak, "traffic": ATTN_DRAM_TRAFFIC_BYTES,
+                     "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this "
+                                       "kernel on this workload; a recorded figure, not measured in this run",
+                     "ms_per_launch": ms_attn, "peak_source": peak_src},
+        "e2e": None if ms_e2e is None else
+               {"value": world * flops / (ms_e2e * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms_e2e,
+                "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": out_bytes, "steps": e2e_steps},
+        "gpu_launches": 2 * args.steps,
+        "clocks": clocks,
+    }
+    return line
 
 
 def run_ours(args, rank, world):
@@ -292,11 +331,27 @@ def run_ours(args, rank, world):
         attn_only()
     ms_attn = time_region(attn_only, args.steps, stream)
 
+    # ---- the same fused step back to back for seconds: the chip reaches its power state, the
+    # clock samples are many, and the figure is set against the sustained cuBLAS peak
+    sustained = None
+    if world == 1 and not args.skip_sustained:
+        sus_steps = int(np.ceil(args.sustained_seconds / (ms * 1e-3)))
+        sus_sampler = ClockSampler(dev, period_s=0.02)
+        ms_sus = time_region(step, sus_steps, stream)
+        sus_clk = sus_sampler.stop()
+        speak, ssrc = measured_peak("bf16_tflops_sustained")
+        sustained = {"ms_per_step": ms_sus, "steps": sus_steps, "seconds": ms_sus * sus_steps * 1e-3,
+                     "value": flops / (ms_sus * 1e-3) / 1e12, "unit": UNIT,
+                     "frac_of_sustained_peak": flops / (ms_sus * 1e-3) / 1e12 / speak, "peak": speak, "peak_source": ssrc,
+                     "clocks": sus_clk, "clock_bins": sus_sampler.bins(),
+                     "ms_x_sm_mhz": None if not sus_clk.get("sm_mhz") else ms_sus * sus_clk["sm_mhz"]}
+
     # ---- one denoise step of the transformer: 8 double-stream calls (text and image streams
     # separate) + 24 single-stream calls (one combined 4608-token stream), as one CUDA graph
-    denoise = None
+    denoise = denoise_cfg = None
     if world == 1 and not args.skip_denoise_step:
-        denoise = denoise_step_leg(f2k, d, dg, dtab, o_t, o_i, ws, ja, B, St, Si, H, D, stream, flops)
+        denoise = denoise_step_leg(d, dg, dtab, o_t, o_i, B, St, Si, H, D, stream, flops, guidance=False)
+        denoise_cfg = denoise_step_leg(d, dg, dtab, o_t, o_i, B, St, Si, H, D, stream, flops, guidance=True)
 
     # ---- end to end through host buffers
     ms_e2e, e2e_steps = None, 0
@@ -323,37 +378,44 @@ def run_ours(args, rank, world):
     status = ja.device_status()
     if status != 0:
         raise RuntimeError("attention kernel reported a device-side error")
+
+    # ---- N > 1: the fixed jobs of the north star, after the headline legs (whose figures are final
+    # by now). A watchdog prints the headline line without them should a job ever stall.
+    strong = None
+    if world > 1 and not args.skip_strong_scaling:
+        hin = None
+        torch.cuda.empty_cache()
+        result = {}
+
+        def headline_only():
+            if rank == 0:
+                result["line"]["strong_scaling"] = {"error": "stalled: abandoned after %d s" % STRONG_SECTION_LIMIT_S}
+                print(json.dumps(result["line"]), flush=True)
+            os._exit(0)
+
+        import threading
+        watchdog = threading.Timer(STRONG_SECTION_LIMIT_S, headline_only)
+        watchdog.daemon = True
+        if rank == 0:
+            result["line"] = _headline_line(args, world, flops, ms, ms_attn, ms_e2e, e2e_steps, d, o_t, o_i, clocks, B, H,
+                                            St, Si, D)
+        watchdog.start()
+        try:
+            strong = strong_scaling_section(rank, world)
+        except Exception as exc:
+            strong = {"error": f"{type(exc).__name__}: {exc}"}
+        watchdog.cancel()
     if rank != 0:
         return None
 
-    peak, peak_src = measured_peak()
-    achieved = flops / (ms_attn * 1e-3) / 1e12
-    in_bytes = sum(x.numel() * 2 for x in d)
-    out_bytes = o_t.numel() * 2 + o_i.numel() * 2
-    line = {
-        "metric": METRIC, "value": world * flops / (ms * 1e-3) / 1e12, "unit": UNIT,
-        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-        "data": "synthetic",
-        "config": {"workload": "s4608 joint attention (512 text + 64x64 image tokens, hd128), "
-                               f"batch {B}, {H} heads per GPU" + (" (heads sharded)" if world > 1 else ""),
-                   "step": "fused QK-RMSNorm + 4-axis RoPE + non-causal attention, one call",
-                   "flops_per_step_per_gpu": flops, "seq": St + Si, "head_dim": D,
-                   "l2": "inputs + outputs + workspace of a step exceed the 126 MB L2 (226 MB)",
-                   "parallelism": f"heads{world}" if world > 1 else "single"},
-        "per_gpu_tflops": flops / (ms * 1e-3) / 1e12,
-        "pct_of_peak": 100.0 * flops / (ms * 1e-3) / 1e12 / peak,
-        "roofline": {"bound": "tensor", "kernel": "attn_fwd_sm100_kernel", "achieved": achieved, "peak": peak,
-                     "unit": UNIT, "frac": achieved / peak, "traffic": ATTN_DRAM_TRAFFIC_BYTES,
-                     "ms_per_launch": ms_attn, "peak_source": peak_src},
-        "e2e": None if ms_e2e is None else
-               {"value": world * flops / (ms_e2e * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms_e2e,
-                "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": out_bytes, "steps": e2e_steps},
-        "gpu_launches": 2 * args.steps,
-        "clocks": clocks,
-    }
+    line = _headline_line(args, world, flops, ms, ms_attn, ms_e2e, e2e_steps, d, o_t, o_i, clocks, B, H, St, Si, D)
+    if strong is not None:
+        line["strong_scaling"] = strong
+    if sustained is not None:
+        line["sustained"] = sustained
     if denoise is not None:
         line["denoise_step"] = denoise
+        line["denoise_step_cfg"] = denoise_cfg
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(p, tabs, flops / H)
     if world == 1 and not args.no_reference_kernel:
@@ -372,113 +434,94 @@ def run_ours(args, rank, world):
     return line
 
 
-def run_seqpar(args, rank, world):
-    """Sequence-parallel attention on the 8704- / 16896-token shapes, batch 1, 32 heads: every rank
-    owns S/world tokens. Step = QK-norm + RoPE of the local Q and K, the pulls of the other ranks'
-    K/V shards by the copy engines (readiness is exchanged as words in the shard buffers, no
-    collective) and the attention kernel that consumes them as they arrive. V is already in the shard buffer (where a
-    V projection would write it). Strong scaling: the total work is fixed."""
+# --------------------------------------------------------------------------------------------
+# Strong-scaling jobs: a fixed job spread over the GPUs by heads, by sequence (K/V shards pulled by
+# the copy engines under the kernel) or by head exchange (sequence outside, heads inside).
+# Each set-up returns the step, the figures that describe it, and a parity check of rank 0's
+# output against the reference's own kernels (rebuilt for sm_100a) on the same inputs.
+# --------------------------------------------------------------------------------------------
+SHAPES = {"s4608_b4": "s4608_b4", "s8704": "s8704_edit", "s16896": "s16896"}
+
+
+def _shape_of(job: str):
+    from f2k_cuda_b200.inputs import WORKLOADS
+    return WORKLOADS[SHAPES[job.rsplit("_", 1)[0]]]
+
+
+def _tables(w):
     import f2k_cuda_b200 as f2k
-    from f2k_cuda_b200.inputs import WORKLOADS, make_problem, token_positions
-    from f2k_cuda_b200.seqpar import SequenceParallelAttention, qk_norm_rope, shard_bounds
-    w = WORKLOADS["s16896" if args.workload.startswith("s16896") else "s8704_edit"]
-    S, H, D = w.seq, w.n_heads, w.head_dim
-    if S % world != 0:
-        raise SystemExit(f"{S} tokens do not split evenly over {world} ranks")
-    per = S // world
-    b, e = shard_bounds(S, world, rank)
-    stream = torch.cuda.current_stream()
-    # this rank's tokens only: positions decide which stream (text or image) a token belongs to
+    from f2k_cuda_b200.inputs import token_positions
     pt, pi = token_positions(w)
-    cos_t, sin_t = f2k.build_rope_4axis_tables((32,) * 4, pt, 2000.0)
-    cos_i, sin_i = f2k.build_rope_4axis_tables((32,) * 4, pi, 2000.0)
-    cos = np.concatenate([cos_t, cos_i])[b:e]
-    sin = np.concatenate([sin_t, sin_i])[b:e]
-    n_txt = max(0, min(e, w.seq_txt) - b)           # text tokens in this shard (they come first)
-    gen = torch.Generator(device="cuda").manual_seed(1234 + rank)
-    mk = lambda: torch.randn(1, per, H, D, device="cuda", generator=gen).to(torch.bfloat16)  # noqa: E731
-    q_raw, k_raw, v = mk(), mk(), mk()
-    p = make_problem(WORKLOADS["s1152"], heads=1)    # only for the four gain vectors
-    g = [dev_bf16(x) for x in p.gammas]
-    dcos, dsin = torch.from_numpy(cos).cuda(), torch.from_numpy(sin).cuda()
-    sp = SequenceParallelAttention(1, per, H, D, world, rank)
-    if not sp.ok():
-        raise RuntimeError(sp.last_error())
-    ok = sp.attach_distributed() if world > 1 else sp.attach_in_process([sp])
+    return (*f2k.build_rope_4axis_tables((32,) * 4, pt, 2000.0), *f2k.build_rope_4axis_tables((32,) * 4, pi, 2000.0))
+
+
+def _gains():
+    from f2k_cuda_b200.inputs import WORKLOADS, make_problem
+    return [dev_bf16(g) for g in make_problem(WORKLOADS["s1152"], heads=1).gammas]
+
+
+def _device_metrics(got, ref):
+    a, b = got.double().flatten(), ref.double().flatten()
+    return {"max_abs": float((a - b).abs().max()), "cosine": float((a @ b) / ((a @ a).sqrt() * (b @ b).sqrt())),
+            "gate": "max_abs <= 2e-2 and cosine >= 0.9999", "against": "the reference's kernels rebuilt for sm_100a, same inputs"}
+
+
+def _reference_streams(ref, streams, B, H, D):
+    """The reference's block sequence (rmsnorm_bf16, rope_4axis_inplace_bf16, then JointAttention or
+    Attention::forward) over one or two streams of raw (q, k, v, gain_q, gain_k, cos, sin)."""
+    L = ref.lib
+    P = lambda t: C.c_void_p(t.data_ptr())  # noqa: E731
+    prepared = []
+    for q, k, v, gq, gk, cos, sin in streams:
+        seq = q.shape[1]
+        q, k = q.clone(), k.clone()
+        rows = B * seq * H
+        pos = ((torch.arange(rows, device="cuda") // H) % seq).to(torch.int32)
+        for x, g in ((q, gq), (k, gk)):
+            if not (L.f2k_ref_rmsnorm_bf16(P(x), P(g), P(x), rows, D, 1e-6, None) and
+                    L.f2k_ref_rope_4axis_inplace_bf16(P(x), P(cos), P(sin), P(pos), rows, D, seq, None)):
+                raise RuntimeError("reference prologue launch failed")
+        prepared.append((q, k, v))
+    outs = [torch.empty_like(q) for q, _, _ in prepared]
+    if len(prepared) == 2:
+        (qt, kt, vt), (qi, ki, vi) = prepared
+        h = L.f2k_ref_joint_create(B, qt.shape[1], qi.shape[1], H, D, 0.0)
+        n = L.f2k_ref_joint_workspace_bytes(h)
+        ws = torch.empty(n, dtype=torch.uint8, device="cuda")
+        ok = L.f2k_ref_joint_ok(h) and L.f2k_ref_joint_forward(h, P(qt), P(kt), P(vt), P(qi), P(ki), P(vi), P(outs[0]),
+                                                               P(outs[1]), P(ws), n, None)
+        torch.cuda.synchronize()
+        L.f2k_ref_joint_destroy(h)
+    else:
+        (q, k, v), = prepared
+        h = L.f2k_ref_attn_create(B, q.shape[1], H, D, 0.0)
+        ok = L.f2k_ref_attn_ok(h) and L.f2k_ref_attn_forward(h, P(q), P(k), P(v), P(outs[0]), None)
+        torch.cuda.synchronize()
+        L.f2k_ref_attn_destroy(h)
     if not ok:
-        raise RuntimeError("attaching the peers' shard buffers failed: " + sp.last_error())
-    qn, o = torch.empty_like(q_raw), torch.empty_like(q_raw)
-    for _ in range(2):                                # V into both buffer sets
-        ks, vs = sp.local_kv()
-        vs.copy_(v)
-        ks.zero_()
-        sp.forward(q_raw, o, overlap=False)
-    torch.cuda.synchronize()
-
-    def norm_rope(x, y, gq_txt, gq_img):
-        okk = True
-        if n_txt > 0:
-            okk &= qk_norm_rope(x[:, :n_txt], y[:, :n_txt], gq_txt, dcos[:n_txt], dsin[:n_txt], 1e-6)
-        if n_txt < per:
-            okk &= qk_norm_rope(x[:, n_txt:], y[:, n_txt:], gq_img, dcos[n_txt:], dsin[n_txt:], 1e-6)
-        return okk
-
-    def step():
-        ks, _ = sp.local_kv()
-        okk = norm_rope(q_raw, qn, g[0], g[2]) and norm_rope(k_raw, ks, g[1], g[3])
-        okk = okk and sp.forward(qn, o, overlap=not args.no_overlap)
-        if not okk:
-            raise RuntimeError(sp.last_error())
-
-    for _ in range(max(args.warmup, 3)):
-        step()
-    if sp.device_status() != 0:
-        raise RuntimeError("attention kernel reported a device-side error during warm-up")
-    sampler = ClockSampler(torch.cuda.current_device()) if rank == 0 else None
-    if world > 1:
-        torch.distributed.barrier()
-    ms = time_region(step, args.steps, stream)
-    if world > 1:
-        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
-        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
-        ms = float(t.item())
-    clocks = sampler.stop() if sampler else None
-    if sp.device_status() != 0:
-        raise RuntimeError("attention kernel reported a device-side error")
-    if rank != 0:
-        return None
-    flops = 4.0 * H * float(S) ** 2 * D                # whole job
-    peak, peak_src = measured_peak()
-    return {
-        "metric": METRIC, "value": flops / (ms * 1e-3) / 1e12, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
-        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"{w.name}: {S} tokens, batch 1, 32 heads, hd128, sequence sharded {per} tokens per GPU",
-                   "step": "QK-RMSNorm + RoPE of the local Q, K; copy-engine pulls of the remote K/V shards "
-                           + ("after which" if args.no_overlap else "under") + " the attention kernel",
-                   "flops_per_step_total": flops, "parallelism": f"seq{world}",
-                   "nvlink_bytes_per_gpu_per_step": 2 * (world - 1) * per * H * D * 2,
-                   "l2": "K/V of all ranks (%.0f MB) exceed the 126 MB L2" % (2 * S * H * D * 2 / 1e6)},
-        "per_gpu_tflops": flops / world / (ms * 1e-3) / 1e12,
-        "pct_of_peak": 100.0 * flops / world / (ms * 1e-3) / 1e12 / peak, "peak_source": peak_src,
-        "e2e": None, "gpu_launches": (4 if 0 < n_txt < per else 2) * args.steps + args.steps, "clocks": clocks,
-    }
+        raise RuntimeError("reference attention launch failed")
+    return outs
 
 
-def run_heads_strong(args, rank, world):
-    """A fixed job (batch-4 1024px step, image-edit shape or 2048px shape) with its 32 heads sharded
-    32/N per GPU: strong scaling, no traffic between the GPUs inside the step. Inputs are drawn on
-    the device (N(0,1), seeded per rank); gains and RoPE tables as in the headline workload."""
+def _gather_tokens(x, world):
+    """[1, per, H, D] shards of all ranks -> [1, world * per, H, D] on every rank."""
+    if world == 1:
+        return x
+    parts = [torch.empty_like(x) for _ in range(world)]
+    torch.distributed.all_gather(parts, x.contiguous())
+    return torch.cat(parts, 1)
+
+
+def setup_heads(job, rank, world, group_world=None):
+    """The job's 32 heads sharded 32/world per GPU: no traffic between the GPUs inside the step.
+    Inputs are drawn on the device (N(0,1), seeded per rank); gains and RoPE tables as in the
+    headline workload."""
     import f2k_cuda_b200 as f2k
-    from f2k_cuda_b200.inputs import WORKLOADS, make_problem, token_positions
-    w = WORKLOADS[{"s4608_b4_heads": "s4608_b4", "s8704_heads": "s8704_edit", "s16896_heads": "s16896"}[args.workload]]
+    w = _shape_of(job)
     B, St, Si, D = w.batch, w.seq_txt, w.seq_img, w.head_dim
     H = w.n_heads // world
-    stream = torch.cuda.current_stream()
-    pt, pi = token_positions(w)
-    dtab = [torch.from_numpy(t).cuda() for t in (*f2k.build_rope_4axis_tables((32,) * 4, pt, 2000.0),
-                                                 *f2k.build_rope_4axis_tables((32,) * 4, pi, 2000.0))]
-    dg = [dev_bf16(g) for g in make_problem(WORKLOADS["s1152"], heads=1).gammas]
+    dtab = [torch.from_numpy(t).cuda() for t in _tables(w)]
+    dg = _gains()
     gen = torch.Generator(device="cuda").manual_seed(4321 + rank)
     mk = lambda n: torch.randn(B, n, H, D, device="cuda", generator=gen).to(torch.bfloat16)  # noqa: E731
     d = [mk(St), mk(St), mk(St), mk(Si), mk(Si), mk(Si)]
@@ -492,111 +535,253 @@ def run_heads_strong(args, rank, world):
         if not ja.forward_fused(*d, dg, dtab, 1e-6, o_t, o_i, ws):
             raise RuntimeError(ja.last_error())
 
-    for _ in range(max(args.warmup, 3)):
-        step()
-    sampler = ClockSampler(torch.cuda.current_device()) if rank == 0 else None
-    if world > 1:
-        torch.distributed.barrier()
-    ms = time_region(step, args.steps, stream)
-    if world > 1:
-        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
-        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
-        ms = float(t.item())
-    clocks = sampler.stop() if sampler else None
-    if ja.device_status() != 0:
-        raise RuntimeError("attention kernel reported a device-side error")
-    if rank != 0:
-        return None
-    flops = 4.0 * B * w.n_heads * float(St + Si) ** 2 * D      # whole job
-    peak, peak_src = measured_peak()
-    return {
-        "metric": METRIC, "value": flops / (ms * 1e-3) / 1e12, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
-        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"{w.name}: {St + Si} tokens, batch {B}, hd128, 32 heads sharded {H} per GPU",
-                   "step": "fused QK-RMSNorm + 4-axis RoPE + non-causal attention, one call",
-                   "flops_per_step_total": flops, "parallelism": f"heads{world}" if world > 1 else "single",
-                   "l2": "Q, K, V, O and workspace of a step (%.0f MB per GPU) exceed the 126 MB L2"
-                         % (6 * B * (St + Si) * H * D * 2 / 1e6)},
-        "per_gpu_tflops": flops / world / (ms * 1e-3) / 1e12,
-        "pct_of_peak": 100.0 * flops / world / (ms * 1e-3) / 1e12 / peak, "peak_source": peak_src,
-        "e2e": None, "gpu_launches": 2 * args.steps, "clocks": clocks,
-    }
+    def parity(ref):
+        r_t, r_i = _reference_streams(ref, [(d[0], d[1], d[2], dg[0], dg[1], dtab[0], dtab[1]),
+                                            (d[3], d[4], d[5], dg[2], dg[3], dtab[2], dtab[3])], B, H, D)
+        return _device_metrics(torch.cat([o_t, o_i], 1), torch.cat([r_t, r_i], 1))
+
+    return {"step": step, "status": ja.device_status, "parity": parity, "launches_per_step": 2,
+            "flops_total": 4.0 * B * w.n_heads * float(St + Si) ** 2 * D, "nvlink_bytes_per_gpu_per_step": 0,
+            "workload": f"{w.name}: {St + Si} tokens, batch {B}, hd128, 32 heads sharded {H} per GPU",
+            "step_text": "fused QK-RMSNorm + 4-axis RoPE + non-causal attention, one call",
+            "parallelism": f"heads{world}" if world > 1 else "single",
+            "l2": "Q, K, V, O and workspace of a step (%.0f MB per GPU) exceed the 126 MB L2"
+                  % (6 * B * (St + Si) * H * D * 2 / 1e6)}
 
 
-def run_headswap(args, rank, world):
-    """Sequence-parallel attention by head exchange on the 8704- / 16896-token shapes, batch 1, 32
-    heads: every rank owns S/world tokens outside and 32/world heads inside. Step = one kernel that
-    normalises + rotates Q, K and scatters Q, K, V by head into the peers' memory, the attention
-    kernel (its epilogue stores each output row into the token owner's memory), and the wait for the
-    other ranks' rows. Strong scaling; no collective and no copy engine in the step."""
-    import f2k_cuda_b200 as f2k
-    from f2k_cuda_b200.headswap import HeadExchangeAttention
-    from f2k_cuda_b200.inputs import WORKLOADS, make_problem, token_positions
-    w = WORKLOADS["s16896" if args.workload.startswith("s16896") else "s8704_edit"]
+def _seq_shard_inputs(w, rank, world):
+    """This rank's tokens of the text||image sequence: raw Q, K, V drawn on the device, the rows of
+    the combined RoPE tables, and how many of the tokens are text (they come first)."""
     S, H, D = w.seq, w.n_heads, w.head_dim
     if S % world != 0 or H % world != 0:
         raise SystemExit(f"{S} tokens / {H} heads do not split evenly over {world} ranks")
     per = S // world
     b, e = rank * per, (rank + 1) * per
-    stream = torch.cuda.current_stream()
-    pt, pi = token_positions(w)
-    cos_t, sin_t = f2k.build_rope_4axis_tables((32,) * 4, pt, 2000.0)
-    cos_i, sin_i = f2k.build_rope_4axis_tables((32,) * 4, pi, 2000.0)
-    dcos = torch.from_numpy(np.concatenate([cos_t, cos_i])[b:e].copy()).cuda()
-    dsin = torch.from_numpy(np.concatenate([sin_t, sin_i])[b:e].copy()).cuda()
+    tabs = _tables(w)
+    cos = np.concatenate([tabs[0], tabs[2]])
+    sin = np.concatenate([tabs[1], tabs[3]])
     gen = torch.Generator(device="cuda").manual_seed(1234 + rank)
     mk = lambda: torch.randn(1, per, H, D, device="cuda", generator=gen).to(torch.bfloat16)  # noqa: E731
     q_raw, k_raw, v = mk(), mk(), mk()
-    g = [dev_bf16(x) for x in make_problem(WORKLOADS["s1152"], heads=1).gammas]
+    return per, b, e, q_raw, k_raw, v, cos, sin, max(0, min(e, w.seq_txt) - b)
+
+
+def setup_seqpar(job, rank, world, overlap=True):
+    """Sequence-parallel attention, batch 1, 32 heads: every rank owns S/world tokens. Step = QK-norm +
+    RoPE of the local Q and K, the pulls of the other ranks' K/V shards by the copy engines (readiness
+    is exchanged as words in the shard buffers, no collective) and the attention kernel that consumes
+    them as they arrive. V is already in the shard buffer (where a V projection would write it)."""
+    from f2k_cuda_b200.seqpar import SequenceParallelAttention, qk_norm_rope
+    w = _shape_of(job)
+    S, H, D = w.seq, w.n_heads, w.head_dim
+    per, b, e, q_raw, k_raw, v, cos, sin, n_txt = _seq_shard_inputs(w, rank, world)
+    g = _gains()
+    dcos, dsin = torch.from_numpy(cos[b:e].copy()).cuda(), torch.from_numpy(sin[b:e].copy()).cuda()
+    sp = SequenceParallelAttention(1, per, H, D, world, rank)
+    if not sp.ok():
+        raise RuntimeError(sp.last_error())
+    if not (sp.attach_distributed() if world > 1 else sp.attach_in_process([sp])):
+        raise RuntimeError("attaching the peers' shard buffers failed: " + sp.last_error())
+    qn, o = torch.empty_like(q_raw), torch.empty_like(q_raw)
+    for _ in range(2):                                # V into both buffer sets
+        ks, vs = sp.local_kv()
+        vs.copy_(v)
+        ks.zero_()
+        sp.forward(q_raw, o, overlap=False)
+    torch.cuda.synchronize()
+
+    def norm_rope(x, y, g_txt, g_img):
+        okk = True
+        if n_txt > 0:
+            okk &= qk_norm_rope(x[:, :n_txt], y[:, :n_txt], g_txt, dcos[:n_txt], dsin[:n_txt], 1e-6)
+        if n_txt < per:
+            okk &= qk_norm_rope(x[:, n_txt:], y[:, n_txt:], g_img, dcos[n_txt:], dsin[n_txt:], 1e-6)
+        return okk
+
+    def step():
+        ks, _ = sp.local_kv()
+        okk = norm_rope(q_raw, qn, g[0], g[2]) and norm_rope(k_raw, ks, g[1], g[3])
+        if not (okk and sp.forward(qn, o, overlap=overlap)):
+            raise RuntimeError(sp.last_error())
+
+    def parity(ref):
+        qa, ka, va = (_gather_tokens(x, world) for x in (q_raw, k_raw, v))      # collective: every rank calls it
+        if rank != 0:
+            return None
+        dc, ds = torch.from_numpy(cos).cuda(), torch.from_numpy(sin).cuda()
+        t = w.seq_txt
+        r_t, r_i = _reference_streams(ref, [(qa[:, :t].contiguous(), ka[:, :t].contiguous(), va[:, :t].contiguous(),
+                                             g[0], g[1], dc[:t], ds[:t]),
+                                            (qa[:, t:].contiguous(), ka[:, t:].contiguous(), va[:, t:].contiguous(),
+                                             g[2], g[3], dc[t:], ds[t:])], 1, H, D)
+        return _device_metrics(o, torch.cat([r_t, r_i], 1)[:, b:e])
+
+    return {"step": step, "status": sp.device_status, "parity": parity,
+            "launches_per_step": (4 if 0 < n_txt < per else 2) + 1, "flops_total": 4.0 * H * float(S) ** 2 * D,
+            "nvlink_bytes_per_gpu_per_step": 2 * (world - 1) * per * H * D * 2,
+            "workload": f"{w.name}: {S} tokens, batch 1, 32 heads, hd128, sequence sharded {per} tokens per GPU",
+            "step_text": "QK-RMSNorm + RoPE of the local Q, K; copy-engine pulls of the remote K/V shards "
+                         + ("under" if overlap else "after which") + " the attention kernel",
+            "parallelism": f"seq{world}", "l2": "K/V of all ranks (%.0f MB) exceed the 126 MB L2" % (2 * S * H * D * 2 / 1e6),
+            "keep": sp}
+
+
+def setup_hx(job, rank, world):
+    """Sequence-parallel attention by head exchange, batch 1, 32 heads: every rank owns S/world tokens
+    outside and 32/world heads inside. Step = one kernel that normalises + rotates Q, K and scatters
+    Q, K, V by head into the peers' memory, the attention kernel (its epilogue stores each output row
+    into the token owner's memory), and the wait for the other ranks' rows. No collective and no
+    copy engine in the step."""
+    from f2k_cuda_b200.headswap import HeadExchangeAttention
+    w = _shape_of(job)
+    S, H, D = w.seq, w.n_heads, w.head_dim
+    per, b, e, q_raw, k_raw, v, cos, sin, _ = _seq_shard_inputs(w, rank, world)
+    g = _gains()
+    dcos, dsin = torch.from_numpy(cos[b:e].copy()).cuda(), torch.from_numpy(sin[b:e].copy()).cuda()
     hx = HeadExchangeAttention(per, H, D, world, rank)
     if not hx.ok():
         raise RuntimeError(hx.last_error())
-    ok = hx.attach_distributed() if world > 1 else hx.attach_in_process([hx])
-    if not ok:
+    if not (hx.attach_distributed() if world > 1 else hx.attach_in_process([hx])):
         raise RuntimeError("attaching the peers' exchange buffers failed: " + hx.last_error())
     if world > 1:
         torch.distributed.barrier()
+    out = [None]
 
     def step():
         # one gain pair for the whole sequence (the single-stream block's call)
-        if not (hx.exchange_in(q_raw, k_raw, v, g[2], g[3], dcos, dsin, 1e-6) and hx.attend()) or hx.output() is None:
+        if not (hx.exchange_in(q_raw, k_raw, v, g[2], g[3], dcos, dsin, 1e-6) and hx.attend()):
+            raise RuntimeError(hx.last_error())
+        out[0] = hx.output()
+        if out[0] is None:
             raise RuntimeError(hx.last_error())
 
-    for _ in range(max(args.warmup, 3)):
-        step()
-    if hx.device_status() != 0:
+    def parity(ref):
+        qa, ka, va = (_gather_tokens(x, world) for x in (q_raw, k_raw, v))
+        if rank != 0:
+            return None
+        dc, ds = torch.from_numpy(cos).cuda(), torch.from_numpy(sin).cuda()
+        (r,) = _reference_streams(ref, [(qa, ka, va, g[2], g[3], dc, ds)], 1, H, D)
+        return _device_metrics(out[0], r[:, b:e])
+
+    return {"step": step, "status": hx.device_status, "parity": parity, "launches_per_step": 2,
+            "flops_total": 4.0 * H * float(S) ** 2 * D,
+            "nvlink_bytes_per_gpu_per_step": 4 * (world - 1) * per * (H // world) * D * 2,
+            "workload": f"{w.name}: {S} tokens, batch 1, 32 heads, hd128, {per} tokens per GPU outside, "
+                        f"{H // world} heads per GPU inside",
+            "step_text": "QK-RMSNorm + RoPE + head scatter into peer memory (one kernel); attention with the "
+                         "epilogue storing into the token owner's memory; wait for the peers' rows",
+            "parallelism": f"headswap{world}",
+            "l2": "Q, K, V, O of a step (%.0f MB per GPU) exceed the 126 MB L2" % (4 * S * (H // world) * D * 2 / 1e6),
+            "keep": hx}
+
+
+def setup_job(job, rank, world, overlap=True):
+    kind = job.rsplit("_", 1)[1]
+    if kind == "heads":
+        return setup_heads(job, rank, world)
+    if kind == "hx":
+        return setup_hx(job, rank, world)
+    return setup_seqpar(job, rank, world, overlap)
+
+
+def time_job(j, steps, warmup, rank, world, sample_clocks=True):
+    """Warm up, then time `steps` steps between barriers; max over ranks. Returns (ms, clocks)."""
+    stream = torch.cuda.current_stream()
+    for _ in range(max(warmup, 3)):
+        j["step"]()
+    if j["status"]() != 0:
         raise RuntimeError("attention kernel reported a device-side error during warm-up")
-    sampler = ClockSampler(torch.cuda.current_device()) if rank == 0 else None
+    sampler = ClockSampler(torch.cuda.current_device()) if rank == 0 and sample_clocks else None
     if world > 1:
         torch.distributed.barrier()
-    ms = time_region(step, args.steps, stream)
+    ms = time_region(j["step"], steps, stream)
     if world > 1:
         t = torch.tensor([ms], device="cuda", dtype=torch.float64)
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
         ms = float(t.item())
     clocks = sampler.stop() if sampler else None
-    if hx.device_status() != 0:
+    if j["status"]() != 0:
         raise RuntimeError("attention kernel reported a device-side error")
+    return ms, clocks
+
+
+def run_strong(args, rank, world):
+    """One strong-scaling job as the whole measurement (--workload <shape>_<heads|seqpar|hx>)."""
+    j = setup_job(args.workload, rank, world, overlap=not args.no_overlap)
+    ms, clocks = time_job(j, args.steps, args.warmup, rank, world)
     if rank != 0:
         return None
-    flops = 4.0 * H * float(S) ** 2 * D                # whole job
+    flops = j["flops_total"]
     peak, peak_src = measured_peak()
     return {
         "metric": METRIC, "value": flops / (ms * 1e-3) / 1e12, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"{w.name}: {S} tokens, batch 1, 32 heads, hd128, {per} tokens per GPU outside, "
-                               f"{H // world} heads per GPU inside",
-                   "step": "QK-RMSNorm + RoPE + head scatter into peer memory (one kernel); attention with the "
-                           "epilogue storing into the token owner's memory; wait for the peers' rows",
-                   "flops_per_step_total": flops, "parallelism": f"headswap{world}",
-                   "nvlink_bytes_per_gpu_per_step": 4 * (world - 1) * per * (H // world) * D * 2,
-                   "l2": "Q, K, V, O of a step (%.0f MB per GPU) exceed the 126 MB L2" % (4 * S * (H // world) * D * 2 / 1e6)},
+        "config": {"workload": j["workload"], "step": j["step_text"], "flops_per_step_total": flops,
+                   "parallelism": j["parallelism"], "nvlink_bytes_per_gpu_per_step": j["nvlink_bytes_per_gpu_per_step"],
+                   "l2": j["l2"]},
         "per_gpu_tflops": flops / world / (ms * 1e-3) / 1e12,
         "pct_of_peak": 100.0 * flops / world / (ms * 1e-3) / 1e12 / peak, "peak_source": peak_src,
-        "e2e": None, "gpu_launches": 2 * args.steps, "clocks": clocks,
+        "e2e": None, "gpu_launches": j["launches_per_step"] * args.steps, "clocks": clocks,
     }
+
+
+STRONG_JOBS = ("s4608_b4_heads", "s16896_heads", "s16896_seqpar", "s16896_hx", "s8704_heads", "s8704_seqpar", "s8704_hx")
+
+
+def strong_scaling_section(rank, world, min_seconds=0.5):
+    """The fixed jobs the north star names, spread over the `world` GPUs of this run three ways
+    (heads, sequence, head exchange), each beside rank 0's own one-GPU time of the same job taken in
+    this same run: efficiency = t1 / (world * t_world). Every timed region lasts at least
+    `min_seconds`. Parity: rank 0's output rows against the reference's kernels on the gathered
+    inputs."""
+    import oracle
+    ref = oracle.load_ref()
+    peak, _ = measured_peak()
+    out = {"min_seconds_per_job": min_seconds, "jobs": {}, "one_gpu": {},
+           "efficiency": "t1 / (n_gpus * ms_per_step): t1 = rank 0 alone, same job, same run, plain fused call"}
+
+    def n_steps(flops_per_gpu):
+        return max(10, int(np.ceil(min_seconds / (flops_per_gpu / 1.0e15))))
+
+    # rank 0 alone: the whole job on one GPU (the other ranks wait at the barrier inside time_job of the next job)
+    t1 = {}
+    for shape in ("s4608_b4", "s16896", "s8704"):
+        if rank == 0:
+            j = setup_heads(shape + "_heads", 0, 1)
+            steps = n_steps(j["flops_total"])
+            ms, clocks = time_job(j, steps, 3, 0, 1)
+            t1[shape] = ms
+            out["one_gpu"][shape] = {"ms_per_step": ms, "steps": steps, "tflops": j["flops_total"] / (ms * 1e-3) / 1e12,
+                                     "clocks": clocks}
+            del j
+            torch.cuda.empty_cache()
+    for job in STRONG_JOBS:
+        rec = {}
+        try:
+            j = setup_job(job, rank, world)
+            steps = n_steps(j["flops_total"] / world)
+            ms, clocks = time_job(j, steps, 3, rank, world)
+            par = j["parity"](ref) if ref is not None else None
+            if rank == 0:
+                shape = job.rsplit("_", 1)[0]
+                rec = {"ms_per_step": ms, "steps": steps, "t1_ms": t1[shape], "efficiency": t1[shape] / (world * ms),
+                       "tflops_total": j["flops_total"] / (ms * 1e-3) / 1e12,
+                       "pct_of_peak_per_gpu": 100.0 * j["flops_total"] / world / (ms * 1e-3) / 1e12 / peak,
+                       "nvlink_bytes_per_gpu_per_step": j["nvlink_bytes_per_gpu_per_step"],
+                       "nvlink_gb_per_s_per_gpu": j["nvlink_bytes_per_gpu_per_step"] / (ms * 1e-3) / 1e9,
+                       "parallelism": j["parallelism"], "workload": j["workload"], "clocks": clocks,
+                       "parity": par if par is not None else "oracle/_ref not built"}
+            del j
+        except Exception as exc:  # one job must not take the others (or the headline) down
+            rec = {"error": f"{type(exc).__name__}: {exc}"}
+        torch.cuda.synchronize()
+        torch.cuda.empty_cache()
+        if world > 1:
+            torch.distributed.barrier()
+        if rank == 0:
+            out["jobs"][job] = rec
+    return out if rank == 0 else None
 
 
 def run_reference(args, rank, world):
@@ -686,7 +871,7 @@ def run_reference(args, rank, world):
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_path, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "s4608 joint attention (512 text + 64x64 image tokens, hd128), batch 1, 32 heads",
+        "config": {"workload": HEADLINE_WORKLOAD,
                    "step": "reference kernels rebuilt for sm_100a: rmsnorm_bf16 x4, rope_4axis_inplace_bf16 x4, "
                            "JointAttention::forward (3 concat + flash_mma_kernel<128> + split)",
                    "flops_per_step_per_gpu": flops, "ranks_used": 1,
@@ -727,12 +912,8 @@ def main():
             line = run_reference(args, rank, world)
         elif args.workload == "s4608":
             line = run_ours(args, rank, world)
-        elif args.workload.endswith("_heads"):
-            line = run_heads_strong(args, rank, world)
-        elif args.workload.endswith("_hx"):
-            line = run_headswap(args, rank, world)
         else:
-            line = run_seqpar(args, rank, world)
+            line = run_strong(args, rank, world)
         if line is not None:
             print(json.dumps(line), flush=True)
     finally:

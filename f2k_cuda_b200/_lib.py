@@ -52,6 +52,18 @@ def _declare(lib: C.CDLL) -> None:
     lib.f2k_attn_forward_fused_host.argtypes = [vp] * 15 + [f, vp, vp, vp]
     lib.f2k_attn_forward_fused_noalloc.restype = i
     lib.f2k_attn_forward_fused_noalloc.argtypes = [C.POINTER(AttnConfig)] + [vp] * 14 + [f, vp, vp, vp, C.c_char_p, sz]
+    lib.f2k_attn_noalloc_device_status.restype = i
+    lib.f2k_attn_noalloc_device_status.argtypes = [C.POINTER(i), C.c_char_p, sz]
+    lib.f2k_attn_set_wait_limits.restype = i
+    lib.f2k_attn_set_wait_limits.argtypes = [vp, C.c_longlong, C.c_longlong]
+    lib.f2k_seqpar_set_wait_limits.restype = i
+    lib.f2k_seqpar_set_wait_limits.argtypes = [vp, C.c_longlong, C.c_longlong]
+    lib.f2k_seqpar_abort.restype = i
+    lib.f2k_seqpar_abort.argtypes = [vp]
+    lib.f2k_hx_set_wait_limits.restype = i
+    lib.f2k_hx_set_wait_limits.argtypes = [vp, C.c_longlong, C.c_longlong]
+    lib.f2k_hx_abort.restype = i
+    lib.f2k_hx_abort.argtypes = [vp]
     lib.f2k_attn_device_status.restype = i
     lib.f2k_attn_device_status.argtypes = [vp, C.POINTER(i)]
     lib.f2k_rmsnorm_bf16.restype = i
@@ -108,8 +120,8 @@ def _declare(lib: C.CDLL) -> None:
 
 def load(path: Path | None = None) -> C.CDLL:
     path = Path(path) if path else LIB_PATH
-    if not path.exists():
-        build()
+    if path == LIB_PATH:
+        build()          # returns at once when the library is newer than every source it is built from
     if not path.exists():
         raise ImportError(f"{path} is missing and could not be built; f2k_cuda_b200 has no fallback path")
     lib = C.CDLL(str(path))

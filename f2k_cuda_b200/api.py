@@ -63,6 +63,10 @@ class _Module:
         lib.f2k_attn_device_status(self._h, C.byref(st))
         return st.value
 
+    def set_wait_limits(self, in_cta_clk: int = 0, peer_clk: int = 0) -> bool:
+        """Limits of the kernels' bounded waits in SM clock cycles (0 = default)."""
+        return lib.f2k_attn_set_wait_limits(self._h, in_cta_clk, peer_clk) == _lib.F2K_OK
+
     # ---- fused calls (no counterpart in the reference classes); a module without a text stream
     # ---- passes None for every *_txt argument
     def fused_workspace_size_bytes(self) -> int:

@@ -69,49 +69,6 @@ constexpr float kLazyThreshold = 8.0f;  // log2 units
 constexpr int kPParts = F2K_OPT_P_PARTS;
 constexpr int kRegsSoftmax = 208, kRegsOther = 88;   // 2*128*208 + 128*88 = 64512 <= 384*168
 
-// Optional phase timing (bring-up builds only, -DF2K_PROFILE_PHASES): CTA (0,0,0) adds the SM
-// clock cycles each role spends per phase into the words after the status word.
-#ifdef F2K_PROFILE_PHASES
-#define PH_DECL long long ph_t = clock64()
-#define PH_MARK(slot)                                                                      \
-    do {                                                                                   \
-        const long long ph_n = clock64();                                                  \
-        if (ph_on) atomicAdd(reinterpret_cast<unsigned long long*>(p.status) + 1 + (slot), \
-                             (unsigned long long)(ph_n - ph_t));                           \
-        ph_t = ph_n;                                                                       \
-    } while (0)
-// like PH_MARK, and also counts the waits longer than 200 cycles (slot + 1) and keeps the longest (slot + 2)
-#define PH_MARK_HIST(slot)                                                                     \
-    do {                                                                                       \
-        const long long ph_n = clock64();                                                      \
-        if (ph_on) {                                                                           \
-            unsigned long long* b_ = reinterpret_cast<unsigned long long*>(p.status) + 1 + (slot); \
-            atomicAdd(b_, (unsigned long long)(ph_n - ph_t));                                  \
-            if (ph_n - ph_t > 200) atomicAdd(b_ + 1, 1ull);                                    \
-            atomicMax(b_ + 2, (unsigned long long)(ph_n - ph_t));                              \
-        }                                                                                      \
-        ph_t = ph_n;                                                                           \
-    } while (0)
-// raw event trace of CTA (0,0,0) for key tiles 8..11: every tracing thread owns a region of the
-// status buffer (plain stores, no atomics on the traced path)
-#define PH_EVDECL(base) int ph_ev = (base)
-#define PH_EVENT(id, jj)                                                                         \
-    do {                                                                                         \
-        if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (threadIdx.x & 31) == 0 &&  \
-            (jj) >= 8 && (jj) < 12) {                                                            \
-            reinterpret_cast<unsigned long long*>(p.status)[ph_ev++] =                           \
-                ((unsigned long long)(id) << 56) | ((unsigned long long)(jj) << 48) |            \
-                ((unsigned long long)clock64() & 0xFFFFFFFFFFFFull);                             \
-        }                                                                                        \
-    } while (0)
-#else
-#define PH_DECL
-#define PH_MARK(slot)
-#define PH_MARK_HIST(slot)
-#define PH_EVDECL(base)
-#define PH_EVENT(id, jj)
-#endif
-
 struct SmemCtl {
     uint64_t q_full[2];
     uint64_t kv_full[kStages];
@@ -188,6 +145,11 @@ attn_fwd_sm100_kernel(const __grid_constant__ AttnParams p) {
     const int head = blockIdx.y;
     const int bidx = blockIdx.z;
     const int n_kv = p.n_kv_tiles;
+    // With an odd number of query tiles the last CTA of a (batch, head) has one tile only: its
+    // second softmax group, and the MMAs that would feed it, are left out.
+    const bool has_t1 = 2 * pair + 1 < p.n_q_tiles;
+    const long long peer_limit = p.peer_wait_limit_clk;
+    const long long wait_limit = p.wait_limit_clk;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < 2; ++i) {
@@ -222,28 +184,24 @@ attn_fwd_sm100_kernel(const __grid_constant__ AttnParams p) {
         if (warp == kLoaderWarp) {
             // ------------------------------ TMA producer ------------------------------
             if (lane == 0) {
-                int issued = 0;
+                int issued = 0, q_issued = 0;
                 bool ok = true;
-                PH_EVDECL(300);
                 for (int t = 0; t < 2 && ok; ++t) {
                     const int qt = 2 * pair + t;
+                    if (qt >= p.n_q_tiles) break;   // odd tile count: the last CTA of a head has one tile
                     int seg, row0, valid;
-                    if (qt < p.n_q_tiles) {
-                        locate_tile<kMaxQSeg>(p.q_tile_start, p.q_len, p.n_qseg, qt, seg, row0, valid);
-                        if (p.q_ready[seg] != nullptr) {   // the segment is written by another GPU's kernel
-                            ok = global_flag_wait(p.q_ready[seg], p.kv_ready_value, abort_flag);
-                            if (!ok) break;
-                            asm volatile("fence.proxy.async.global;" ::: "memory");
-                        }
-                    } else {  // odd tile count: the spare tile reads zeros (out of bounds)
-                        seg = 0;
-                        row0 = ((p.q_len[0] + kTileM - 1) / kTileM) * kTileM;
+                    locate_tile<kMaxQSeg>(p.q_tile_start, p.q_len, p.n_qseg, qt, seg, row0, valid);
+                    if (p.q_ready[seg] != nullptr) {   // the segment is written by another GPU's kernel
+                        ok = global_flag_wait(p.q_ready[seg], p.kv_ready_value, abort_flag, peer_limit);
+                        if (!ok) break;
+                        asm volatile("fence.proxy.async.global;" ::: "memory");
                     }
                     const uint32_t bar = smem_u32(&ctl->q_full[t]);
                     const uint32_t dst = smem + kSmemQ + t * kTileBytes;
                     mbar_arrive_expect_tx(bar, kTileBytes);
                     tma_load_4d(dst, &p.tm_q[seg], bar, 0, head, row0, bidx);
                     tma_load_4d(dst + kBoxBytes, &p.tm_q[seg], bar, 64, head, row0, bidx);
+                    ++q_issued;
                 }
                 for (int j = 0; j < n_kv && ok; ++j) {
                     int seg, row0, valid;
@@ -252,7 +210,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ AttnParams p) {
                         // first tile of a segment that is being copied in: wait for its arrival word,
                         // then order the copy engine's writes before this thread's TMA reads
                         ok = global_flag_wait(p.kv_ready[seg] + head / max(1, p.kv_ready_heads_per_group),
-                                              p.kv_ready_value, abort_flag);
+                                              p.kv_ready_value, abort_flag, peer_limit);
                         if (!ok) break;
                         asm volatile("fence.proxy.async.global;" ::: "memory");
                     }
@@ -260,21 +218,14 @@ attn_fwd_sm100_kernel(const __grid_constant__ AttnParams p) {
                     for (int kv = 0; kv < 2; ++kv) {
                         const int slot = issued % kStages;
                         const uint32_t par = (issued / kStages) & 1;
-                        PH_EVENT(1 + kv, j);   // loader: starts waiting for the slot of K_j (1) / V_j (2)
-                        ok = mbar_wait(smem_u32(&ctl->kv_empty[slot]), par ^ 1u, abort_flag);
+                        ok = mbar_wait(smem_u32(&ctl->kv_empty[slot]), par ^ 1u, abort_flag, wait_limit);
                         if (!ok) break;
-                        PH_EVENT(3 + kv, j);   // loader: slot free, copy issued
                         const uint32_t bar = smem_u32(&ctl->kv_full[slot]);
                         const uint32_t dst = smem + kSmemRing + slot * kTileBytes;
                         const CUtensorMap* tm = kv == 0 ? &p.tm_k[seg] : &p.tm_v[seg];
-#ifdef F2K_EXP_NOLOAD   // timing experiment only: no K/V traffic at all (results are garbage)
-                        (void)dst; (void)tm;
-                        mbar_arrive(bar);
-#else
                         mbar_arrive_expect_tx(bar, kTileBytes);
                         tma_load_4d(dst, tm, bar, 0, head, row0, bidx);
                         tma_load_4d(dst + kBoxBytes, tm, bar, 64, head, row0, bidx);
-#endif
                         ++issued;
                     }
                 }
@@ -282,7 +233,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ AttnParams p) {
                     // Leaving early: let the copies this thread started land first.
                     const long long lim = 40000000ll;  // ~20 ms each, still bounded
                     volatile uint32_t never = 0;
-                    for (int t = 0; t < 2; ++t) mbar_wait(smem_u32(&ctl->q_full[t]), 0, &never, lim);
+                    for (int t = 0; t < q_issued; ++t) mbar_wait(smem_u32(&ctl->q_full[t]), 0, &never, lim);
                     for (int i = max(0, issued - kStages); i < issued; ++i)
                         mbar_wait(smem_u32(&ctl->kv_full[i % kStages]), (i / kStages) & 1, &never, lim);
                 }
@@ -301,7 +252,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ AttnParams p) {
                 // Ring slot of K_j is 2j, of V_j is 2j+1.
                 auto slot_off16 = [&](int n) { return (uint32_t)(n % kStages) * (kTileBytes >> 4); };
                 auto wait_uniform = [&](uint32_t bar, uint32_t parity) {
-                    return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag)) != 0;
+                    return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, wait_limit)) != 0;
                 };
                 auto wait_full = [&](int n) {
                     return wait_uniform(bar_full0 + (n % kStages) * 8, (n / kStages) & 1);
@@ -322,48 +273,33 @@ attn_fwd_sm100_kernel(const __grid_constant__ AttnParams p) {
                     return true;
                 };
 
-#ifdef F2K_PROFILE_PHASES
-                const bool ph_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0;
-#endif
-                PH_DECL;
-                PH_EVDECL(64);
                 for (int j = 0; j < n_kv; ++j) {
                     // S0_j
-                    PH_EVENT(10, j);   // mma: starts waiting for K_j
                     if (!(ok = wait_full(2 * j))) break;
-                    PH_EVENT(11, j);   // mma: K_j there
                     if (j == 0 && !(ok = wait_uniform(smem_u32(&ctl->q_full[0]), 0))) break;
-                    PH_MARK_HIST(24);   // waiting for K_j (+ count of long waits, longest)
                     tc_fence_after_sync();
                     issue_qk(tmem + kColS0, q0_desc, k_desc0 + slot_off16(2 * j));
                     umma_commit(smem_u32(&ctl->s_full[0]));
-                    PH_EVENT(12, j);   // mma: S0_j issued
-                    PH_MARK(17);   // issuing S0
-                    // PV1_{j-1}
-                    if (j > 0) {
-                        if (!(ok = issue_pv(1, j - 1))) break;
-                        release(2 * j - 1);
+                    if (has_t1) {
+                        // PV1_{j-1}
+                        if (j > 0) {
+                            if (!(ok = issue_pv(1, j - 1))) break;
+                            release(2 * j - 1);
+                        }
+                        // S1_j
+                        if (j == 0 && !(ok = wait_uniform(smem_u32(&ctl->q_full[1]), 0))) break;
+                        tc_fence_after_sync();
+                        issue_qk(tmem + kColS1, q1_desc, k_desc0 + slot_off16(2 * j));
+                        umma_commit(smem_u32(&ctl->s_full[1]));
                     }
-                    PH_EVENT(13, j);   // mma: PV1_{j-1} issued, V_{j-1} released
-                    PH_MARK(18);   // waiting for P1 + issuing PV1
-                    // S1_j
-                    if (j == 0 && !(ok = wait_uniform(smem_u32(&ctl->q_full[1]), 0))) break;
-                    tc_fence_after_sync();
-                    issue_qk(tmem + kColS1, q1_desc, k_desc0 + slot_off16(2 * j));
-                    umma_commit(smem_u32(&ctl->s_full[1]));
                     release(2 * j);
-                    PH_EVENT(14, j);   // mma: S1_j issued, K_j released
-                    PH_MARK(19);   // issuing S1
                     // PV0_j
                     if (!(ok = wait_full(2 * j + 1))) break;
-                    PH_EVENT(15, j);   // mma: V_j there
-                    PH_MARK(20);   // waiting for V_j
                     if (!(ok = issue_pv(0, j))) break;
+                    if (!has_t1) release(2 * j + 1);
                     if (j == n_kv - 1) umma_commit(smem_u32(&ctl->o_full[0]));
-                    PH_EVENT(16, j);   // mma: PV0_j issued
-                    PH_MARK(21);   // waiting for P0 + issuing PV0
                 }
-                if (ok && n_kv > 0) {
+                if (ok && n_kv > 0 && has_t1) {
                     // PV1 of the last tile
                     ok = issue_pv(1, n_kv - 1);
                     if (ok) {
@@ -396,23 +332,16 @@ attn_fwd_sm100_kernel(const __grid_constant__ AttnParams p) {
         float l_sum = 0.0f;
         bool ok = true;
 
-#ifdef F2K_PROFILE_PHASES
-        const bool ph_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (warp & 3) == 0 && lane == 0;
-        const int ph_base = t * 8;
-#endif
-        PH_DECL;
-        PH_EVDECL(160 + t * 64);
         int kv_seg = 0, kv_row0 = 0;
-        for (int j = 0; j < n_kv; ++j) {
+        const int n_iter = (t == 0 || has_t1) ? n_kv : 0;
+        for (int j = 0; j < n_iter; ++j) {
             const int valid = min(kTileN, p.kv_len[kv_seg] - kv_row0);
             kv_row0 += kTileN;
             if (kv_row0 >= p.kv_len[kv_seg]) { kv_row0 = 0; ++kv_seg; }
 
-            ok = mbar_wait(smem_u32(&ctl->s_full[t]), j & 1, abort_flag);
+            ok = mbar_wait(smem_u32(&ctl->s_full[t]), j & 1, abort_flag, wait_limit);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
-            if ((warp & 3) == 0) PH_EVENT(20 + t, j);   // softmax t: S_j seen
-            PH_MARK(ph_base + 0);   // waiting for S
             tc_fence_after_sync();
 
             // The row is fetched in two halves: the maxima of the first 64 scores are folded while
@@ -437,7 +366,6 @@ attn_fwd_sm100_kernel(const __grid_constant__ AttnParams p) {
                 row_max64<true>(&s[0], mx);
                 tmem_wait_ld();
             }
-            PH_MARK(ph_base + 1);   // S -> registers
             if (valid < kTileN) {
 #pragma unroll
                 for (int i = 64; i < 128; ++i)
@@ -466,7 +394,6 @@ attn_fwd_sm100_kernel(const __grid_constant__ AttnParams p) {
                 }
             }
 
-            PH_MARK(ph_base + 2);   // row max, vote, (rare) rescale
             // P = 2^(c s - c m_ref), rounded to bf16 into the first 64 columns of S_t (two keys
             // per column); the row sum keeps the unrounded values.
             const float neg_mc = -m_ref * c;
@@ -483,33 +410,28 @@ attn_fwd_sm100_kernel(const __grid_constant__ AttnParams p) {
                     tmem_wait_st();
                     tc_fence_before_sync();
                     mbar_arrive(smem_u32(&ctl->p_full[t][0]) + pending * 8);
-                    if ((warp & 3) == 0) PH_EVENT(30 + t * 4 + pending, j);   // softmax t: part handed over
                     pending = -1;
                 }
                 exp_chunk16<F2K_OPT_POLY_OF8>(&s[q * 32 + 16], pk + 8, c, neg_mc, sum);
                 tmem_st_x16(tS + q * 16, pk);
                 if ((q + 1) % (4 / kPParts) == 0) pending = (q + 1) / (4 / kPParts) - 1;
             }
-            PH_MARK(ph_base + 3);   // exponentials
             tmem_wait_st();
             tc_fence_before_sync();
             mbar_arrive(smem_u32(&ctl->p_full[t][kPParts - 1]));
-            if ((warp & 3) == 0) PH_EVENT(30 + t * 4 + kPParts - 1, j);
-            PH_MARK(ph_base + 4);   // last store drain + hand-over
             l_sum += (sum[0] + sum[1]) + (sum[2] + sum[3]);
         }
 
         // ------------------------------ epilogue ------------------------------------
-        if (ok && n_kv > 0) {
-            ok = mbar_wait(smem_u32(&ctl->o_full[t]), 0, abort_flag);
+        if (ok && n_iter > 0) {
+            ok = mbar_wait(smem_u32(&ctl->o_full[t]), 0, abort_flag, wait_limit);
             ok = __all_sync(0xffffffffu, ok);
         }
-        if (ok && n_kv > 0) {
+        if (ok && n_iter > 0) {
             tc_fence_after_sync();
             const int qt = 2 * pair + t;
             int seg = 0, row0 = 0, valid = 0;
-            if (qt < p.n_q_tiles)
-                locate_tile<kMaxQSeg>(p.q_tile_start, p.q_len, p.n_qseg, qt, seg, row0, valid);
+            locate_tile<kMaxQSeg>(p.q_tile_start, p.q_len, p.n_qseg, qt, seg, row0, valid);
             const int r = (warp & 3) * 32 + lane;  // row inside the tile
             const float inv = 1.0f / (l_sum + 1e-30f);
             __nv_bfloat16* orow = static_cast<__nv_bfloat16*>(p.o_ptr[seg]) +
@@ -543,7 +465,8 @@ attn_fwd_sm100_kernel(const __grid_constant__ AttnParams p) {
     if (threadIdx.x == 0 && *abort_flag != 0u && p.status != nullptr)
         atomicOr(p.status, (int)kStatusWaitExpired);
     if (threadIdx.x == 0 && p.done_counter != nullptr)   // all output rows of this CTA are stored (barrier above)
-        grid_done_publish(p.done_counter, gridDim.x * gridDim.y * gridDim.z, p.done_flag, p.n_done, p.done_value);
+        grid_done_publish(p.done_counter, gridDim.x * gridDim.y * gridDim.z, p.done_flag, p.fail_flag, p.n_done,
+                          p.done_value, p.status);
     if (warp == kMmaWarp) {
         tc_fence_after_sync();
         tmem_dealloc(tmem, kTmemCols);
@@ -572,9 +495,18 @@ cudaError_t attn_fwd_prepare() {
     return cudaSuccess;
 }
 
-cudaError_t attn_fwd_launch(const AttnParams& p, cudaStream_t stream) {
+cudaError_t attn_fwd_launch(const AttnParams& params, cudaStream_t stream) {
     cudaError_t e = attn_fwd_prepare();
     if (e != cudaSuccess) return e;
+    AttnParams p = params;
+    if (p.wait_limit_clk <= 0) p.wait_limit_clk = kDefaultWaitClk;
+    if (p.peer_wait_limit_clk <= 0) p.peer_wait_limit_clk = kDefaultPeerWaitClk;
+    // An in-CTA wait may sit behind a peer wait of the loader (a softmax group waits for S, the MMA
+    // warp for K, the loader for the word), so it has to outlast it where peer words are in use.
+    bool peer_words = false;
+    for (int i = 0; i < kMaxKvSeg; ++i) peer_words |= p.kv_ready[i] != nullptr;
+    for (int i = 0; i < kMaxQSeg; ++i) peer_words |= p.q_ready[i] != nullptr;
+    if (peer_words) p.wait_limit_clk += p.peer_wait_limit_clk;
     const size_t smem = attn_fwd_smem_bytes();
     dim3 grid((p.n_q_tiles + 1) / 2, p.n_heads, p.batch);
     attn_fwd_sm100_kernel<<<grid, kThreads, smem, stream>>>(p);

@@ -9,6 +9,7 @@
 // segment's own TMA tensor map, so a tile never straddles two allocations.
 #pragma once
 
+#include <cstddef>
 #include <cstdint>
 #include <cuda.h>
 
@@ -24,7 +25,18 @@ constexpr int kMaxKvSeg = 8;
 enum AttnStatus : int {
     kStatusOk          = 0,
     kStatusWaitExpired = 1,  // a bounded wait ran out; the output is invalid
+    kStatusPeerFailed  = 2,  // head exchange: another rank's kernel gave up; rows it owed are stale
+    kStatusAborted     = 4,  // the host released the stream waits of a step (f2k_*_abort)
 };
+
+constexpr size_t kStatusBytes = 256;   // every status allocation: the word, padded to the tensor alignment
+
+// Limits of the bounded waits, in SM clock cycles (about 1.9 GHz). A wait inside the CTA (mbarrier:
+// a TMA copy, an MMA, another role of the same CTA) has nothing slower than HBM behind it. A wait
+// on a word that a copy engine or another GPU writes also covers the skew between the rank
+// processes, which the host decides, so its default is much longer.
+constexpr long long kDefaultWaitClk     = 2000000000ll;    // ~1 s
+constexpr long long kDefaultPeerWaitClk = 40000000000ll;   // ~20 s
 
 struct AttnParams {
     // 4-D tensor maps, dims (fastest first): head_dim, head, token, batch;
@@ -53,6 +65,9 @@ struct AttnParams {
 
     int* status;                      // device word, AttnStatus bits OR-ed in
 
+    long long wait_limit_clk;         // bounded waits inside the CTA (0 = kDefaultWaitClk)
+    long long peer_wait_limit_clk;    // bounded waits on kv_ready / q_ready words (0 = kDefaultPeerWaitClk)
+
     // Sequence-parallel use: key/value segment i may still be on its way into this GPU's memory
     // when the kernel starts (a copy engine is bringing it over NVLink, one group of
     // kv_ready_heads_per_group heads at a time). When kv_ready[i] is not null the TMA producer of
@@ -73,8 +88,12 @@ struct AttnParams {
     // n_done words done_flag[] (words in this and in the peers' memory) after every output row of
     // the launch has been written: outputs may go straight into other GPUs' buffers (o_ptr), and
     // this tells their owners. The counter is left at zero for the next launch.
+    // If a CTA of the launch gave up on a wait, its output rows were not written: the last CTA then
+    // stores done_value to fail_flag[] (same owners as done_flag[]) BEFORE it publishes done, so that
+    // nobody who sees "done" can miss the failure.
     unsigned int* done_counter;
     unsigned int* done_flag[8];
+    unsigned int* fail_flag[8];
     int           n_done;
     unsigned int  done_value;
 };

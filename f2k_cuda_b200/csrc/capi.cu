@@ -21,13 +21,16 @@ namespace {
 using namespace f2k;
 
 constexpr size_t kAlign = 256;
-constexpr size_t kStatusBytes = 4096;   // the status word; bring-up builds keep phase counters behind it
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                    const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                    const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The kernels read Q, K, gains and tables with 16-byte loads: a pointer that is not 16-byte aligned
+// would be a misaligned-address fault on the GPU, so it is refused here, before any launch.
+inline bool misaligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) != 0; }
 
 // The driver entry point is fetched through the runtime so that the library carries no
 // link-time dependency on libcuda.
@@ -82,6 +85,7 @@ struct f2k_attn {
     std::string     err;
     int             device = -1;
     int*            d_status = nullptr;
+    long long       wait_clk = 0, peer_wait_clk = 0;   // 0 = the defaults of attn_params.h
 
     // Descriptors of the last forward call; rebuilt only when a pointer changes.
     const void* last_in[6] = {};
@@ -170,6 +174,8 @@ int build_params(f2k_attn* h, AttnParams& p, const QSeg* qs, int nq, const KvSeg
     p.batch      = c.batch;
     p.scale_log2 = h->scale * 1.4426950408889634f;
     p.status     = h->d_status;
+    p.wait_limit_clk      = h->wait_clk;
+    p.peer_wait_limit_clk = h->peer_wait_clk;
     return F2K_OK;
 }
 
@@ -462,14 +468,19 @@ int f2k_attn_forward_fused_strided(f2k_attn* h, const void* q_txt, const void* k
         for (long long v : all)
             if (v != 0 && (v < dense || v % 8 != 0))
                 return fail(h, F2K_ERR_INVALID, "token stride must be 0 or a multiple of 8 that is >= n_heads * 128");
-        const void* raw[4] = {q_txt, k_txt, q_img, k_img};
-        for (const void* ptr : raw)
-            if ((reinterpret_cast<uintptr_t>(ptr) & 15u) != 0)
-                return fail(h, F2K_ERR_INVALID, "tensor base pointer is not 16-byte aligned");
     }
     if (!q_img || !k_img || !gamma_q_img || !gamma_k_img || !cos_img || !sin_img ||
         (has_txt && (!q_txt || !k_txt || !gamma_q_txt || !gamma_k_txt || !cos_txt || !sin_txt)))
         return fail(h, F2K_ERR_INVALID, "null tensor pointer");
+    {
+        // V and O are checked where their tensor maps / output pointers are set up (build_params)
+        const void* vec[12] = {q_img, k_img, gamma_q_img, gamma_k_img, cos_img, sin_img,
+                               q_txt, k_txt, gamma_q_txt, gamma_k_txt, cos_txt, sin_txt};
+        for (int i = 0; i < (has_txt ? 12 : 6); ++i)
+            if (misaligned16(vec[i]))
+                return fail(h, F2K_ERR_INVALID,
+                            "Q, K, gain and RoPE-table pointers must be 16-byte aligned (the kernels use 16-byte loads)");
+    }
 
     uint8_t* ws = static_cast<uint8_t*>(workspace);
     void* qn_txt = ws;
@@ -542,6 +553,12 @@ int f2k_attn_forward_fused_host(f2k_attn* h, const void* hq_txt, const void* hk_
     if (!gamma_q_img || !gamma_k_img || !cos_img || !sin_img ||
         (has_txt && (!gamma_q_txt || !gamma_k_txt || !cos_txt || !sin_txt)))
         return fail(h, F2K_ERR_INVALID, "null tensor pointer");
+    {
+        const void* vec[8] = {gamma_q_img, gamma_k_img, cos_img, sin_img, gamma_q_txt, gamma_k_txt, cos_txt, sin_txt};
+        for (int i = 0; i < (has_txt ? 8 : 4); ++i)
+            if (misaligned16(vec[i]))
+                return fail(h, F2K_ERR_INVALID, "gain and RoPE-table pointers must be 16-byte aligned");
+    }
     if (want_rows && c.batch == 1)
         return host_row_chunks(h, hq_txt, hk_txt, hv_txt, hq_img, hk_img, hv_img, gamma_q_txt, gamma_k_txt,
                                gamma_q_img, gamma_k_img, cos_txt, sin_txt, cos_img, sin_img, eps, ho_txt, ho_img,
@@ -670,12 +687,24 @@ int f2k_attn_device_status(f2k_attn* h, int* status_out) {
     return F2K_OK;
 }
 
+int f2k_attn_set_wait_limits(f2k_attn* h, long long in_cta_clk, long long peer_clk) {
+    if (!h || !h->valid) return F2K_ERR_INVALID;
+    if (in_cta_clk < 0 || peer_clk < 0) return fail(h, F2K_ERR_INVALID, "wait limits must not be negative");
+    h->wait_clk = in_cta_clk;
+    h->peer_wait_clk = peer_clk;
+    h->have_params = false;          // the limits travel inside the cached launch parameters
+    h->chunk_params.clear();
+    for (f2k_attn* ch : h->child) f2k_attn_set_wait_limits(ch, in_cta_clk, peer_clk);
+    return F2K_OK;
+}
+
 int f2k_rmsnorm_bf16(const void* x, const void* gamma, void* y, int rows, int dim, float eps,
                      void* stream) {
     // Same refusals as the reference wrapper (kernels/rmsnorm.cu:76-77).
     if (rows <= 0 || dim <= 0) return F2K_ERR_INVALID;
     if (dim % 8 != 0) return F2K_ERR_INVALID;
     if (!x || !gamma || !y) return F2K_ERR_INVALID;
+    if (misaligned16(x) || misaligned16(gamma) || misaligned16(y)) return F2K_ERR_INVALID;   // 16-byte loads
     return rmsnorm_rows_launch(x, gamma, y, rows, dim, eps, static_cast<cudaStream_t>(stream)) == cudaSuccess
                ? F2K_OK : F2K_ERR_CUDA;
 }
@@ -687,6 +716,14 @@ int f2k_rope_4axis_inplace_bf16(void* x, const float* cos_table, const float* si
     if (rows <= 0 || head_dim <= 0 || (head_dim & 1)) return F2K_ERR_INVALID;
     if (head_dim > 512) return F2K_ERR_INVALID;
     if (!x || !cos_table || !sin_table || !pos_ids || seq_max <= 0) return F2K_ERR_INVALID;
+    // head_dim 128 rows go through 16-byte loads (x, and a token's 64 cos / sin values as float4);
+    // other head dims through 4-byte loads of x
+    if (head_dim == 128 ? (misaligned16(x) || misaligned16(cos_table) || misaligned16(sin_table))
+                        : (reinterpret_cast<uintptr_t>(x) & 3u) != 0)
+        return F2K_ERR_INVALID;
+    if ((reinterpret_cast<uintptr_t>(cos_table) & 3u) || (reinterpret_cast<uintptr_t>(sin_table) & 3u) ||
+        (reinterpret_cast<uintptr_t>(pos_ids) & 3u))
+        return F2K_ERR_INVALID;
     return rope4_rows_launch(x, cos_table, sin_table, pos_ids, rows, head_dim, seq_max,
                              static_cast<cudaStream_t>(stream)) == cudaSuccess
                ? F2K_OK : F2K_ERR_CUDA;
@@ -733,16 +770,6 @@ int f2k_build_rope_4axis_tables(const int* axes_dim, int n_axes, const int* posi
     return F2K_OK;
 }
 
-const char* f2k_attn_version(void) { return "f2k_attn sm_100a 0.1"; }
-
-#ifdef F2K_PROFILE_PHASES
-// Bring-up builds only: copies the phase counters (64-bit words after the status word) out.
-int f2k_attn_debug_phases(f2k_attn* h, unsigned long long* out, int n) {
-    if (!h || !h->valid || n <= 0 || (size_t)(n + 1) * 8 > kStatusBytes) return F2K_ERR_INVALID;
-    if (cudaDeviceSynchronize() != cudaSuccess) return F2K_ERR_CUDA;
-    return cudaMemcpy(out, reinterpret_cast<unsigned long long*>(h->d_status) + 1, (size_t)n * 8,
-                      cudaMemcpyDeviceToHost) == cudaSuccess ? F2K_OK : F2K_ERR_CUDA;
-}
-#endif
+const char* f2k_attn_version(void) { return "f2k_attn sm_100a 0.2"; }
 
 }  // extern "C"

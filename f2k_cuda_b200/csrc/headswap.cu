@@ -23,7 +23,7 @@
 //
 // One allocation per rank, exported to the peers by CUDA IPC:
 //     [2 sets] { Qh, Kh, Vh : [world * s_loc, heads/world, 128] ; O : [s_loc, heads, 128] }
-//     control words: arrived[2][world], done[2][world], two counters.
+//     control words: arrived[2][world], done[2][world], two counters, failed[2][world].
 
 #include "f2k_attn.h"
 
@@ -64,7 +64,13 @@ struct f2k_hx {
     int*   d_status = nullptr;
     std::vector<unsigned char*> peer;
     unsigned int epoch = 0;
-    bool   exchanged = false, attended = false;
+    enum Phase { kIdle, kExchanged, kAttended } phase = kIdle;   // exchange_in -> attend -> output -> ...
+    long long wait_clk = 0, peer_wait_clk = 0;                   // 0 = the defaults of attn_params.h
+    bool   aborted = false;
+    unsigned int fail_reported = 0;                              // step whose peer failure was already reported
+    cudaStream_t abort_stream = nullptr;
+    using WriteValue32Fn = CUresult (*)(CUstream, CUdeviceptr, cuuint32_t, unsigned int);
+    WriteValue32Fn write32 = nullptr;
     EncodeTiledFn encode = nullptr;
     WaitValue32Fn wait32 = nullptr;
     AttnParams params[2];                    // per buffer set; only the call number changes between steps
@@ -78,6 +84,9 @@ struct f2k_hx {
     unsigned int* arrived(unsigned char* base, int set, int src) const { return words(base) + set * 8 + src; }
     unsigned int* done(unsigned char* base, int set, int src) const { return words(base) + 16 + set * 8 + src; }
     unsigned int* counter(int i) const { return words(buf) + 32 + i; }
+    // failed[set][src]: rank src stores the step number here when a CTA of its attention kernel gave
+    // up, before it publishes done[set][src]: its heads of this rank's rows were not all written
+    unsigned int* failed(unsigned char* base, int set, int src) const { return words(base) + 40 + set * 8 + src; }
 };
 
 namespace {
@@ -132,7 +141,8 @@ int f2k_hx_create(const f2k_seqpar_config* cfg, f2k_hx** out) {
     if (major != 10) return fail(h, F2K_ERR_UNSUPPORTED, "this library contains sm_100a code only");
     h->encode = reinterpret_cast<EncodeTiledFn>(driver_entry("cuTensorMapEncodeTiled"));
     h->wait32 = reinterpret_cast<WaitValue32Fn>(driver_entry("cuStreamWaitValue32"));
-    if (!h->encode || !h->wait32) return fail(h, F2K_ERR_CUDA, "driver entry points unavailable");
+    h->write32 = reinterpret_cast<f2k_hx::WriteValue32Fn>(driver_entry("cuStreamWriteValue32"));
+    if (!h->encode || !h->wait32 || !h->write32) return fail(h, F2K_ERR_CUDA, "driver entry points unavailable");
     e = attn_fwd_prepare();
     if (e == cudaSuccess) e = qk_prologue_prepare();
     if (e != cudaSuccess) return fail_cuda(h, "kernel load", e);
@@ -140,9 +150,11 @@ int f2k_hx_create(const f2k_seqpar_config* cfg, f2k_hx** out) {
     if (e != cudaSuccess) return fail_cuda(h, "cudaMalloc(exchange buffer)", e);
     e = cudaMemset(h->buf + h->flags_off, 0, 256);
     if (e != cudaSuccess) return fail_cuda(h, "cudaMemset(flags)", e);
-    e = cudaMalloc(reinterpret_cast<void**>(&h->d_status), 256);
-    if (e == cudaSuccess) e = cudaMemset(h->d_status, 0, 256);
+    e = cudaMalloc(reinterpret_cast<void**>(&h->d_status), kStatusBytes);
+    if (e == cudaSuccess) e = cudaMemset(h->d_status, 0, kStatusBytes);
     if (e != cudaSuccess) return fail_cuda(h, "cudaMalloc(status)", e);
+    e = cudaStreamCreateWithFlags(&h->abort_stream, cudaStreamNonBlocking);
+    if (e != cudaSuccess) return fail_cuda(h, "cudaStreamCreate", e);
     h->peer.assign(cfg->world, nullptr);
     h->peer[cfg->rank] = h->buf;
     h->valid = true;
@@ -151,6 +163,7 @@ int f2k_hx_create(const f2k_seqpar_config* cfg, f2k_hx** out) {
 
 void f2k_hx_destroy(f2k_hx* h) {
     if (!h) return;
+    if (h->abort_stream) cudaStreamDestroy(h->abort_stream);
     if (h->d_status) cudaFree(h->d_status);
     if (h->buf) cudaFree(h->buf);
     delete h;
@@ -182,9 +195,17 @@ int f2k_hx_exchange_in(f2k_hx* h, const void* q_raw, const void* k_raw, const vo
     if (!h || !h->valid) return F2K_ERR_INVALID;
     if (!q_raw || !k_raw || !v || !gamma_q || !gamma_k || !cos_local || !sin_local)
         return fail(h, F2K_ERR_INVALID, "null tensor pointer");
+    for (const void* ptr : {q_raw, k_raw, v, gamma_q, gamma_k, static_cast<const void*>(cos_local),
+                            static_cast<const void*>(sin_local)})
+        if ((reinterpret_cast<uintptr_t>(ptr) & 15u) != 0)
+            return fail(h, F2K_ERR_INVALID, "tensor, gain and table pointers must be 16-byte aligned");
     const f2k_seqpar_config& c = h->cfg;
     for (int r = 0; r < c.world; ++r)
         if (!h->peer[r]) return fail(h, F2K_ERR_INVALID, "peers not attached");
+    // The two buffer sets are safe to reuse only if every step is completed: the stream wait of
+    // output() is what keeps this rank from overwriting a set its peers still write into.
+    if (h->phase != f2k_hx::kIdle)
+        return fail(h, F2K_ERR_INVALID, "exchange_in before the previous step's attend and output");
     h->epoch += 1;
     const int set = h->epoch & 1;
     QkvScatterParams p;
@@ -204,13 +225,13 @@ int f2k_hx_exchange_in(f2k_hx* h, const void* q_raw, const void* k_raw, const vo
     p.eps = eps;
     const cudaError_t e = qkv_scatter_launch(p, static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return fail_cuda(h, "exchange kernel launch", e);
-    h->exchanged = true;
+    h->phase = f2k_hx::kExchanged;
     return F2K_OK;
 }
 
 int f2k_hx_attend(f2k_hx* h, void* stream) {
     if (!h || !h->valid) return F2K_ERR_INVALID;
-    if (!h->exchanged) return fail(h, F2K_ERR_INVALID, "attend without exchange_in");
+    if (h->phase != f2k_hx::kExchanged) return fail(h, F2K_ERR_INVALID, "attend without exchange_in");
     const f2k_seqpar_config& c = h->cfg;
     const int set = h->epoch & 1;
     AttnParams& p = h->params[set];
@@ -233,6 +254,7 @@ int f2k_hx_attend(f2k_hx* h, void* stream) {
             p.q_tile_start[s] = p.kv_tile_start[s] = s * tiles_per_seg;
             if (s != c.rank) p.q_ready[s] = p.kv_ready[s] = h->arrived(h->buf, set, s);
             p.done_flag[s] = h->done(h->peer[s], set, c.rank);
+            p.fail_flag[s] = h->failed(h->peer[s], set, c.rank);
         }
         // this rank's own rows come from the kernel just before on the same stream: no wait needed
         p.q_tile_start[c.world] = p.kv_tile_start[c.world] = c.world * tiles_per_seg;
@@ -249,22 +271,24 @@ int f2k_hx_attend(f2k_hx* h, void* stream) {
     }
     p.kv_ready_value = h->epoch;
     p.done_value = h->epoch;
+    p.wait_limit_clk      = h->wait_clk;
+    p.peer_wait_limit_clk = h->peer_wait_clk;
     const cudaError_t e = attn_fwd_launch(p, static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return fail_cuda(h, "attention launch", e);
-    h->exchanged = false;
-    h->attended = true;
+    h->phase = f2k_hx::kAttended;
     return F2K_OK;
 }
 
 int f2k_hx_output(f2k_hx* h, void** o_local, void* stream) {
     if (!h || !h->valid) return F2K_ERR_INVALID;
-    if (!h->attended) return fail(h, F2K_ERR_INVALID, "output without attend");
+    if (h->phase != f2k_hx::kAttended) return fail(h, F2K_ERR_INVALID, "output without attend");
     const int set = h->epoch & 1;
     for (int s = 0; s < h->cfg.world; ++s)
         if (h->wait32(static_cast<CUstream>(stream), reinterpret_cast<CUdeviceptr>(h->done(h->buf, set, s)), h->epoch,
                       0 /* CU_STREAM_WAIT_VALUE_GEQ */) != CUDA_SUCCESS)
             return fail(h, F2K_ERR_CUDA, "cuStreamWaitValue32 failed");
     if (o_local) *o_local = h->part(h->buf, set, 3);
+    h->phase = f2k_hx::kIdle;
     return F2K_OK;
 }
 
@@ -276,8 +300,52 @@ int f2k_hx_device_status(f2k_hx* h, int* status_out) {
     e = cudaMemcpy(&st, h->d_status, sizeof st, cudaMemcpyDeviceToHost);
     if (e != cudaSuccess) return fail_cuda(h, "status read", e);
     if (st != 0) cudaMemset(h->d_status, 0, sizeof st);
+    // did a peer give up during the last step? its kernel says so in this rank's control words
+    if (h->epoch > 0 && h->fail_reported != h->epoch) {
+        unsigned int words[8] = {};
+        const int set = h->epoch & 1;
+        e = cudaMemcpy(words, h->failed(h->buf, set, 0), sizeof words, cudaMemcpyDeviceToHost);
+        if (e != cudaSuccess) return fail_cuda(h, "status read", e);
+        for (int s = 0; s < h->cfg.world; ++s)
+            if (words[s] == h->epoch) st |= kStatusPeerFailed;
+        if (st & kStatusPeerFailed) h->fail_reported = h->epoch;      // reported once, like the status word
+    }
+    if (h->aborted) {
+        st |= kStatusAborted;
+        h->aborted = false;
+    }
     if (status_out) *status_out = st;
-    if (st != 0) return fail(h, F2K_ERR_DEVICE, "a bounded wait inside the attention kernel expired");
+    if (st & kStatusAborted) return fail(h, F2K_ERR_DEVICE, "the step was aborted by the host: a peer never delivered");
+    if (st & kStatusWaitExpired) return fail(h, F2K_ERR_DEVICE, "a bounded wait inside the attention kernel expired");
+    if (st & kStatusPeerFailed)
+        return fail(h, F2K_ERR_DEVICE, "a peer's attention kernel gave up: some heads of this rank's output rows are stale");
+    return F2K_OK;
+}
+
+int f2k_hx_set_wait_limits(f2k_hx* h, long long in_cta_clk, long long peer_clk) {
+    if (!h || !h->valid) return F2K_ERR_INVALID;
+    if (in_cta_clk < 0 || peer_clk < 0) return fail(h, F2K_ERR_INVALID, "wait limits must not be negative");
+    h->wait_clk = in_cta_clk;
+    h->peer_wait_clk = peer_clk;
+    return F2K_OK;
+}
+
+// output() parks the stream on waits for every rank's "done" word. If a peer is gone the words
+// never come. This writes them for the current step from the host side, on a stream of its own,
+// so that the parked waits fall through; the step's output is invalid and device_status reports
+// F2K_ERR_DEVICE once. Does not synchronise with the caller's stream.
+int f2k_hx_abort(f2k_hx* h) {
+    if (!h || !h->valid) return F2K_ERR_INVALID;
+    if (h->epoch == 0) return F2K_OK;
+    const int set = h->epoch & 1;
+    for (int s = 0; s < h->cfg.world; ++s)
+        if (h->write32(reinterpret_cast<CUstream>(h->abort_stream), reinterpret_cast<CUdeviceptr>(h->done(h->buf, set, s)),
+                       h->epoch, 0) != CUDA_SUCCESS)
+            return fail(h, F2K_ERR_CUDA, "cuStreamWriteValue32 failed");
+    const cudaError_t e = cudaStreamSynchronize(h->abort_stream);
+    if (e != cudaSuccess) return fail_cuda(h, "abort stream", e);
+    h->aborted = true;
+    h->phase = f2k_hx::kIdle;
     return F2K_OK;
 }
 

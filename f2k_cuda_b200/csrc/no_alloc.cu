@@ -1,5 +1,5 @@
 // f2k_attn_forward_fused_noalloc: the fused call (per-head RMSNorm + RoPE, then joint
-// attention) for callers that must not allocate device memory.
+// attention) for callers that must not allocate device memory, and the reader of its status word.
 //
 // Who that is: code that runs where the CUDA allocator is off limits - a real-time loop that
 // may not take the allocator's locks or risk its latency, a plug-in whose host application
@@ -9,20 +9,29 @@
 // the workspace f2k_attn_forward_fused wants.
 //
 // What replaces the workspace: a fixed array in the library's own device image
-// (`g_scratch`, 32 MiB). It exists on every GPU that loads the library, from load to exit,
-// whether or not this entry point is ever called. It holds the status word and the
-// normalised + rotated copies of Q and K that the prologue kernel hands to the attention
-// kernel. Shapes that need more are refused.
+// (`g_scratch`, 32 MiB). It holds the status word and the normalised + rotated copies of Q and K
+// that the prologue kernel hands to the attention kernel. Shapes that need more are refused.
+//
+// When the 32 MiB are taken. The array belongs to this file's device module. The CUDA runtime
+// loads a module into a context when something of it is first used there (lazy loading, the
+// default since CUDA 12.2; with CUDA_MODULE_LOADING=EAGER it happens when the context is
+// created). Device memory for the array is reserved at that moment - for this library, inside
+// the first call of either entry point of this file on a device - and is held until the
+// process exits. That first call is therefore the one that can fail for lack of memory, and a
+// caller that hands all device memory out at start-up has to make it BEFORE doing so:
+// f2k_attn_noalloc_device_status(NULL, ...) is enough. After it, no call of this file
+// allocates, frees or loads anything.
 //
 // On the host `g_scratch` is only a stand-in for the symbol: the device address is obtained
-// with cudaGetSymbolAddress, once per device, on that device, the first time this entry point
-// runs there. That first call should therefore come before any stream capture begins.
+// with cudaGetSymbolAddress, once per device, on that device, in that first call, which should
+// therefore also come before any stream capture begins.
 //
 // Every call uses the same array and finds whatever the previous call left in it. The status
-// word is the only part that has to start at zero and is cleared on the stream at the start of
-// each call; the Q/K copies are overwritten in full before they are read. Two calls whose GPU
-// work can overlap (different streams, or different host threads) race on the array: keep the
-// calls of one device on one stream, or serialise them yourself.
+// word is the only part that has to start at zero: it is cleared once when the device is set
+// up and again by f2k_attn_noalloc_device_status when it reads a non-zero value, so a failure
+// stays visible until it is read. The Q/K copies are overwritten in full before they are read.
+// Two calls whose GPU work can overlap (different streams, or different host threads) race on
+// the array: keep the calls of one device on one stream, or serialise them yourself.
 
 #include "f2k_attn.h"
 
@@ -38,8 +47,7 @@ namespace {
 using namespace f2k;
 
 constexpr size_t kScratchBytes = 32u << 20;   // the stated maximum: 32 MiB per GPU
-constexpr size_t kStatusBytes  = 256;         // status word, padded so the tensors stay 256-aligned
-constexpr size_t kAlign        = 256;
+constexpr size_t kAlign        = 256;         // kStatusBytes (attn_params.h) keeps the tensors 256-aligned
 
 static __device__ __align__(256) unsigned char g_scratch[kScratchBytes];
 
@@ -60,8 +68,9 @@ int fail(char* errbuf, size_t errbuf_len, int code, const char* msg) {
     return code;
 }
 
-// Once per device, with that device current: device address of the scratch array and the
-// driver's tensor-map encoder. Neither call allocates.
+// Once per device, with that device current: device address of the scratch array (this is what
+// makes the runtime load the module and reserve the array), the driver's tensor-map encoder,
+// the kernels' one-time configuration, and a zero status word.
 int setup_device(int dev, char* errbuf, size_t errbuf_len) {
     std::lock_guard<std::mutex> lock(g_setup_mutex);
     PerDevice& d = g_dev[dev];
@@ -78,8 +87,24 @@ int setup_device(int dev, char* errbuf, size_t errbuf_len) {
     const cudaError_t e2 = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
     if (e2 != cudaSuccess || q != cudaDriverEntryPointSuccess || fn == nullptr)
         return fail(errbuf, errbuf_len, F2K_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    if (attn_fwd_prepare() != cudaSuccess || qk_prologue_prepare() != cudaSuccess)
+        return fail(errbuf, errbuf_len, F2K_ERR_CUDA, "loading the kernels failed");
+    if (cudaMemset(ptr, 0, kStatusBytes) != cudaSuccess)
+        return fail(errbuf, errbuf_len, F2K_ERR_CUDA, "clearing the status word failed");
     d.scratch = static_cast<unsigned char*>(ptr);
     d.encode  = reinterpret_cast<decltype(d.encode)>(fn);
+    return F2K_OK;
+}
+
+// Current device, checked: index in range and compute capability 10.x.
+int current_device(int* dev_out, char* errbuf, size_t errbuf_len) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices)
+        return fail(errbuf, errbuf_len, F2K_ERR_CUDA, "cudaGetDevice failed");
+    int major = 0;
+    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess || major != 10)
+        return fail(errbuf, errbuf_len, F2K_ERR_UNSUPPORTED, "this library contains sm_100a code only");
+    *dev_out = dev;
     return F2K_OK;
 }
 
@@ -115,6 +140,14 @@ extern "C" int f2k_attn_forward_fused_noalloc(
     if (!q_img || !k_img || !v_img || !o_img || !gamma_q_img || !gamma_k_img || !cos_img || !sin_img ||
         (has_txt && (!q_txt || !k_txt || !v_txt || !o_txt || !gamma_q_txt || !gamma_k_txt || !cos_txt || !sin_txt)))
         return fail(errbuf, errbuf_len, F2K_ERR_INVALID, "null tensor pointer");
+    {
+        // 16-byte loads and stores everywhere: refuse here what would fault on the GPU
+        const void* vec[16] = {q_img, k_img, v_img, o_img, gamma_q_img, gamma_k_img, cos_img, sin_img,
+                               q_txt, k_txt, v_txt, o_txt, gamma_q_txt, gamma_k_txt, cos_txt, sin_txt};
+        for (int i = 0; i < (has_txt ? 16 : 8); ++i)
+            if ((reinterpret_cast<uintptr_t>(vec[i]) & 15u) != 0)
+                return fail(errbuf, errbuf_len, F2K_ERR_INVALID, "tensor, gain and table pointers must be 16-byte aligned");
+    }
 
     const size_t bt = align_up((size_t)cfg->batch * cfg->seq_txt * cfg->n_heads * kHeadDim * 2, kAlign);
     const size_t bi = align_up((size_t)cfg->batch * cfg->seq_img * cfg->n_heads * kHeadDim * 2, kAlign);
@@ -129,12 +162,8 @@ extern "C" int f2k_attn_forward_fused_noalloc(
     }
 
     int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices)
-        return fail(errbuf, errbuf_len, F2K_ERR_CUDA, "cudaGetDevice failed");
-    int major = 0;
-    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess || major != 10)
-        return fail(errbuf, errbuf_len, F2K_ERR_UNSUPPORTED, "this library contains sm_100a code only");
-    const int rc = setup_device(dev, errbuf, errbuf_len);
+    int rc = current_device(&dev, errbuf, errbuf_len);
+    if (rc == F2K_OK) rc = setup_device(dev, errbuf, errbuf_len);
     if (rc != F2K_OK) return rc;
     const PerDevice& d = g_dev[dev];
 
@@ -146,9 +175,9 @@ extern "C" int f2k_attn_forward_fused_noalloc(
     void* kn_img = base + kStatusBytes + 2 * bt + bi;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
 
-    // The array keeps what the last call left: the status word is the one thing that must be zero.
-    if (cudaMemsetAsync(status, 0, kStatusBytes, s) != cudaSuccess)
-        return fail(errbuf, errbuf_len, F2K_ERR_CUDA, "clearing the status word failed");
+    // The array keeps what the last call left. Nothing has to be cleared here: the Q/K copies are
+    // written in full by the prologue kernel before the attention kernel reads them, and the status
+    // word is zero unless an earlier call failed and nobody has read it yet.
 
     QkPrologueParams pp;
     std::memset(&pp, 0, sizeof pp);
@@ -208,5 +237,28 @@ extern "C" int f2k_attn_forward_fused_noalloc(
         return fail(errbuf, errbuf_len, F2K_ERR_CUDA, "prologue launch failed");
     if (attn_fwd_launch(ap, s) != cudaSuccess)
         return fail(errbuf, errbuf_len, F2K_ERR_CUDA, "attention launch failed");
+    return F2K_OK;
+}
+
+// Reads the status word of the allocation-free call on the current device and clears it when it
+// is not zero. Synchronises the device. status_out may be NULL. Allocates nothing; on its first
+// call on a device it does the same one-time set-up as the forward call.
+extern "C" int f2k_attn_noalloc_device_status(int* status_out, char* errbuf, size_t errbuf_len) {
+    if (errbuf && errbuf_len) errbuf[0] = '\0';
+    int dev = 0;
+    int rc = current_device(&dev, errbuf, errbuf_len);
+    if (rc == F2K_OK) rc = setup_device(dev, errbuf, errbuf_len);
+    if (rc != F2K_OK) return rc;
+    int st = 0;
+    if (cudaDeviceSynchronize() != cudaSuccess ||
+        cudaMemcpy(&st, g_dev[dev].scratch, sizeof st, cudaMemcpyDeviceToHost) != cudaSuccess)
+        return fail(errbuf, errbuf_len, F2K_ERR_CUDA, "reading the status word failed");
+    if (st != 0 && cudaMemset(g_dev[dev].scratch, 0, sizeof st) != cudaSuccess)
+        return fail(errbuf, errbuf_len, F2K_ERR_CUDA, "clearing the status word failed");
+    if (status_out) *status_out = st;
+    if (st != 0)
+        return fail(errbuf, errbuf_len, F2K_ERR_DEVICE,
+                    "a bounded wait inside the attention kernel expired: the outputs of the calls since the last "
+                    "status read must not be used");
     return F2K_OK;
 }

@@ -15,18 +15,6 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
-__device__ __forceinline__ bool elect_one() {
-    uint32_t pred = 0;
-    asm volatile(
-        "{\n\t"
-        ".reg .pred P;\n\t"
-        "elect.sync _|P, 0xffffffff;\n\t"
-        "selp.u32 %0, 1, 0, P;\n\t"
-        "}\n"
-        : "=r"(pred));
-    return pred != 0;
-}
-
 // ----------------------------------------------------------------------------
 // mbarrier
 // ----------------------------------------------------------------------------
@@ -67,8 +55,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // try_wait (reading a timer on every miss would sit on the critical path of every
 // hand-over between the roles).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
-                                          volatile uint32_t* abort_flag,
-                                          long long limit_cycles = 2000000000ll) {
+                                          volatile uint32_t* abort_flag, long long limit_cycles) {
     long long t0 = 0;
     for (uint32_t spins = 1;; ++spins) {
         if (mbar_try_wait(bar, parity)) return true;
@@ -89,8 +76,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
 // operation, a kernel on another GPU - sets to `value` (or to the value of a later call: the
 // comparison is "not before", modulo 2^32). Same contract as mbar_wait.
 __device__ __forceinline__ bool global_flag_wait(const unsigned int* flag, unsigned int value,
-                                                 volatile uint32_t* abort_flag,
-                                                 long long limit_cycles = 2000000000ll) {
+                                                 volatile uint32_t* abort_flag, long long limit_cycles) {
     long long t0 = 0;
     for (uint32_t spins = 1;; ++spins) {
         unsigned int v;
@@ -117,15 +103,23 @@ __device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) 
 }
 
 // Called by one thread of every CTA after a CTA-wide barrier that follows the CTA's last global
-// store: the last CTA of the grid to arrive publishes `value` to the `n` words. The counter
-// (zero before the launch) is zero again afterwards.
+// store: the last CTA of the grid to arrive publishes `value` to the `n` words flags[]. When
+// `failed` (a status word some CTA of this launch may have set before it arrived here) is not
+// zero, `value` goes to fail_flags[] first. The counter (zero before the launch) is zero again
+// afterwards.
 __device__ __forceinline__ void grid_done_publish(unsigned int* counter, unsigned int n_ctas,
-                                                  unsigned int* const* flags, int n, unsigned int value) {
+                                                  unsigned int* const* flags, unsigned int* const* fail_flags,
+                                                  int n, unsigned int value, const int* failed) {
     __threadfence_system();
     const unsigned int seen = atomicAdd(counter, 1u);
     if (seen == n_ctas - 1u) {
         atomicExch(counter, 0u);
         __threadfence_system();
+        if (failed != nullptr && *reinterpret_cast<const volatile int*>(failed) != 0) {
+            for (int i = 0; i < n; ++i)
+                if (fail_flags[i] != nullptr) st_release_sys(fail_flags[i], value);
+            __threadfence_system();
+        }
         for (int i = 0; i < n; ++i) st_release_sys(flags[i], value);
     }
 }
@@ -133,9 +127,6 @@ __device__ __forceinline__ void grid_done_publish(unsigned int* counter, unsigne
 // ----------------------------------------------------------------------------
 // TMA (tiled, 4-D, global -> shared, completion on an mbarrier). One destination CTA.
 // ----------------------------------------------------------------------------
-__device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
-    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");
-}
 __device__ __forceinline__ void tma_load_4d(uint32_t dst_smem, const void* tmap, uint32_t bar,
                                             int c0, int c1, int c2, int c3) {
     asm volatile(
@@ -199,20 +190,6 @@ __device__ __forceinline__ void tmem_st_x32(uint32_t taddr, const uint32_t (&r)[
           "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
           "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
         : "memory");
-}
-// Narrow variants (8 columns) for rarely taken paths that must not cost registers.
-__device__ __forceinline__ void tmem_ld_x8(uint32_t taddr, uint32_t (&r)[8]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-                   "=r"(r[7])
-                 : "r"(taddr)
-                 : "memory");
-}
-__device__ __forceinline__ void tmem_st_x8(uint32_t taddr, const uint32_t (&r)[8]) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
-                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]),
-                   "r"(r[6]), "r"(r[7])
-                 : "memory");
 }
 __device__ __forceinline__ void tmem_st_x16(uint32_t taddr, const uint32_t (&r)[16]) {
     asm volatile(
@@ -336,25 +313,6 @@ __device__ __forceinline__ void add2(float& d0, float& d1, float a0, float a1, f
         : "=f"(d0), "=f"(d1)
         : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
 }
-// 2^x for a pair of arguments on the FMA pipe instead of the special-function unit:
-// round-to-nearest split x = n + f with the 1.5*2^23 trick, cubic fit of 2^f on [-0.5, 0.5]
-// (relative error < 1e-4, far inside bf16 resolution), exponent patched in with one integer
-// multiply-add. Arguments are clamped at -126 (result flushes towards 0 below that).
-__device__ __forceinline__ void ex2_poly2(float& r0, float& r1, float x0, float x1) {
-    constexpr float kMagic = 12582912.0f;  // 1.5 * 2^23
-    x0 = fmaxf(x0, -126.0f);
-    x1 = fmaxf(x1, -126.0f);
-    float t0, t1, n0, n1, f0, f1, p0, p1;
-    add2(t0, t1, x0, x1, kMagic, kMagic);
-    add2(n0, n1, t0, t1, -kMagic, -kMagic);
-    fma2(f0, f1, n0, n1, -1.0f, -1.0f, x0, x1);
-    fma2(p0, p1, f0, f1, 0.0550886838f, 0.0550886838f, 0.242604051f, 0.242604051f);
-    fma2(p0, p1, p0, p1, f0, f1, 0.693276242f, 0.693276242f);
-    fma2(p0, p1, p0, p1, f0, f1, 0.99992894f, 0.99992894f);
-    r0 = __uint_as_float(__float_as_uint(t0) * (1u << 23) + __float_as_uint(p0));
-    r1 = __uint_as_float(__float_as_uint(t1) * (1u << 23) + __float_as_uint(p1));
-}
-
 __device__ __forceinline__ float ex2_approx(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));

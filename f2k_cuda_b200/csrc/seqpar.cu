@@ -1,5 +1,6 @@
-// Sequence-parallel ("ring") joint attention across the GPUs of one NVLink/NVSwitch box, and the
-// stand-alone entry point of the QK prologue kernel it uses.
+// Sequence-parallel joint attention across the GPUs of one NVLink/NVSwitch box as an all-gather of
+// the K/V shards by pull (peers are visited in ring order; nothing rotates), and the stand-alone
+// entry point of the QK prologue kernel it uses.
 //
 // The reference has no multi-GPU code at all (one process, one GPU, batch 1); this layer is new.
 // Tokens are sharded by rank: rank r holds Q, K, V of its `seq_local` tokens. Every rank needs
@@ -84,6 +85,10 @@ struct f2k_seqpar {
     cudaEvent_t pulled = nullptr;
     EncodeTiledFn  encode = nullptr;
     WriteValue32Fn write32 = nullptr;
+
+    long long wait_clk = 0, peer_wait_clk = 0;   // 0 = the defaults of attn_params.h
+    bool aborted = false;               // f2k_seqpar_abort released the stream waits of the current step
+    cudaStream_t abort_stream = nullptr;
 
     bool peer_write32 = true;           // stream writes straight into a peer's words work here
     unsigned char* k_slot(unsigned char* base, int set, int slot) const {
@@ -170,12 +175,13 @@ int f2k_seqpar_create(const f2k_seqpar_config* cfg, f2k_seqpar** out) {
     if (e != cudaSuccess) return fail_cuda(h, "cudaMalloc(shards)", e);
     e = cudaMemset(h->buf + h->flags_off, 0, h->total_bytes - h->flags_off);
     if (e != cudaSuccess) return fail_cuda(h, "cudaMemset(flags)", e);
-    e = cudaMalloc(reinterpret_cast<void**>(&h->d_status), 256);
-    if (e == cudaSuccess) e = cudaMemset(h->d_status, 0, 256);
+    e = cudaMalloc(reinterpret_cast<void**>(&h->d_status), kStatusBytes);
+    if (e == cudaSuccess) e = cudaMemset(h->d_status, 0, kStatusBytes);
     if (e != cudaSuccess) return fail_cuda(h, "cudaMalloc(status)", e);
     e = cudaEventCreateWithFlags(&h->pulled, cudaEventDisableTiming);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->written, cudaEventDisableTiming);
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&h->own_copy_stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&h->abort_stream, cudaStreamNonBlocking);
     if (e != cudaSuccess) return fail_cuda(h, "cudaEventCreate/cudaStreamCreate", e);
     h->peer.assign(cfg->world, nullptr);
     h->peer[cfg->rank] = h->buf;
@@ -188,6 +194,7 @@ void f2k_seqpar_destroy(f2k_seqpar* h) {
     if (h->pulled) cudaEventDestroy(h->pulled);
     if (h->written) cudaEventDestroy(h->written);
     if (h->own_copy_stream) cudaStreamDestroy(h->own_copy_stream);
+    if (h->abort_stream) cudaStreamDestroy(h->abort_stream);
     if (h->d_status) cudaFree(h->d_status);
     if (h->buf) cudaFree(h->buf);
     delete h;
@@ -224,6 +231,8 @@ int f2k_seqpar_forward(f2k_seqpar* h, const void* q_local, void* o_local, int ov
                        void* compute_stream, void* copy_stream) {
     if (!h || !h->valid) return F2K_ERR_INVALID;
     if (!q_local || !o_local) return fail(h, F2K_ERR_INVALID, "null tensor pointer");
+    if ((reinterpret_cast<uintptr_t>(q_local) & 15u) || (reinterpret_cast<uintptr_t>(o_local) & 15u))
+        return fail(h, F2K_ERR_INVALID, "q_local and o_local must be 16-byte aligned");
     const f2k_seqpar_config& c = h->cfg;
     for (int r = 0; r < c.world; ++r)
         if (!h->peer[r]) return fail(h, F2K_ERR_INVALID, "peers not attached");
@@ -291,6 +300,8 @@ int f2k_seqpar_forward(f2k_seqpar* h, const void* q_local, void* o_local, int ov
     p.batch = c.batch;
     p.scale_log2 = h->scale * 1.4426950408889634f;
     p.status = h->d_status;
+    p.wait_limit_clk      = h->wait_clk;
+    p.peer_wait_limit_clk = h->peer_wait_clk;
 
     if (c.world > 1) {
         const cudaError_t we = cudaEventRecord(h->written, cs);   // everything before this call on cs: K/V written
@@ -376,8 +387,45 @@ int f2k_seqpar_device_status(f2k_seqpar* h, int* status_out) {
     e = cudaMemcpy(&st, h->d_status, sizeof st, cudaMemcpyDeviceToHost);
     if (e != cudaSuccess) return fail_cuda(h, "status read", e);
     if (st != 0) cudaMemset(h->d_status, 0, sizeof st);
+    if (h->aborted) {
+        st |= kStatusAborted;
+        h->aborted = false;
+    }
     if (status_out) *status_out = st;
+    if (st & kStatusAborted)
+        return fail(h, F2K_ERR_DEVICE, "the step was aborted by the host: a peer never announced its K/V");
     if (st != 0) return fail(h, F2K_ERR_DEVICE, "a bounded wait inside the attention kernel expired");
+    return F2K_OK;
+}
+
+int f2k_seqpar_set_wait_limits(f2k_seqpar* h, long long in_cta_clk, long long peer_clk) {
+    if (!h || !h->valid) return F2K_ERR_INVALID;
+    if (in_cta_clk < 0 || peer_clk < 0) return fail(h, F2K_ERR_INVALID, "wait limits must not be negative");
+    h->wait_clk = in_cta_clk;
+    h->peer_wait_clk = peer_clk;
+    return F2K_OK;
+}
+
+// The copy stream of a step is parked on stream waits for the peers' "written" words. If a peer is
+// gone those words never come, and neither the stream nor anything that synchronises with it
+// (device_status, destroy) would return. This writes the awaited words of the current step from the
+// host side, on a stream of its own, so that the parked waits fall through: the pulls then copy
+// whatever the peers' slots hold (mapped memory, stale values) and the arrival words are written.
+// The step's output is invalid; device_status reports F2K_ERR_DEVICE once. Does not synchronise
+// with the compute or copy stream.
+int f2k_seqpar_abort(f2k_seqpar* h) {
+    if (!h || !h->valid) return F2K_ERR_INVALID;
+    if (h->epoch == 0) return F2K_OK;            // nothing was ever queued
+    const int set = h->epoch & 1;
+    for (int r = 0; r < h->cfg.world; ++r) {
+        if (r == h->cfg.rank) continue;
+        if (h->write32(reinterpret_cast<CUstream>(h->abort_stream),
+                       reinterpret_cast<CUdeviceptr>(h->ready(h->buf, set, r)), h->epoch, 0) != CUDA_SUCCESS)
+            return fail(h, F2K_ERR_CUDA, "cuStreamWriteValue32 failed");
+    }
+    const cudaError_t e = cudaStreamSynchronize(h->abort_stream);
+    if (e != cudaSuccess) return fail_cuda(h, "abort stream", e);
+    h->aborted = true;
     return F2K_OK;
 }
 
@@ -406,6 +454,9 @@ int f2k_qk_norm_rope_bf16(const void* x, void* y, const void* gamma, const float
                           const float* sin_table, int batch, int seq, int n_heads, float eps, void* stream) {
     if (!x || !y || !gamma || !cos_table || !sin_table) return F2K_ERR_INVALID;
     if (batch <= 0 || seq <= 0 || n_heads <= 0) return F2K_ERR_INVALID;
+    for (const void* ptr : {x, static_cast<const void*>(y), gamma, static_cast<const void*>(cos_table),
+                            static_cast<const void*>(sin_table)})
+        if ((reinterpret_cast<uintptr_t>(ptr) & 15u) != 0) return F2K_ERR_INVALID;   // the kernel uses 16-byte accesses
     QkPrologueParams pp;
     std::memset(&pp, 0, sizeof pp);
     pp.job[0].x = x; pp.job[0].y = y; pp.job[0].gamma = gamma;

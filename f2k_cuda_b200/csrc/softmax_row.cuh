@@ -1,8 +1,8 @@
 // Per-row softmax arithmetic of the attention kernel: a thread owns one query row of a
 // 128-key tile in registers (fp32 scores as loaded from tensor memory).
 //
-//   row_max64/128   maximum of the scores (8 independent chains)
-//   exp_chunk32     P = 2^(c*s + neg_mc) for 32 scores -> 16 packed bf16 pairs, and the sum of
+//   row_max64       maximum of 64 scores folded into 8 independent chains
+//   exp_chunk16     P = 2^(c*s + neg_mc) for 16 scores -> 8 packed bf16 pairs, and the sum of
 //                   the unrounded values (four partial sums)
 //
 // 2^x comes from two places so that neither pipe is the bottleneck: the special-function
@@ -32,13 +32,6 @@ __device__ __forceinline__ float row_max_finish(const float (&m)[8]) {
     using namespace f2k::ptx;
     return fmaxf(fmax3(m[0], m[1], m[2]), fmax3(fmax3(m[3], m[4], m[5]), m[6], m[7]));
 }
-__device__ __forceinline__ float row_max128(const uint32_t (&s)[128]) {
-    float m[8];
-    row_max64<true>(&s[0], m);
-    row_max64<false>(&s[64], m);
-    return row_max_finish(m);
-}
-
 // 2^x for a pair on the FMA pipe. x = n + f by the 1.5*2^23 rounding trick, cubic fit of 2^f on
 // [-0.5, 0.5], exponent patched in with an integer shift-add. x is clamped at -126 so that the
 // exponent arithmetic cannot wrap (the result is then ~2^-126, i.e. nothing).
@@ -84,13 +77,6 @@ __device__ __forceinline__ void exp_chunk16(const uint32_t* s, uint32_t* pk, flo
         pk[i / 2 + 0] = pack_bf16x2(p0, p1);
         pk[i / 2 + 1] = pack_bf16x2(p2, p3);
     }
-}
-
-template <int kPolyOf8>
-__device__ __forceinline__ void exp_chunk32(const uint32_t* s, uint32_t (&pk)[16], float c,
-                                            float neg_mc, float (&sum)[4]) {
-    exp_chunk16<kPolyOf8>(s, pk, c, neg_mc, sum);
-    exp_chunk16<kPolyOf8>(s + 16, pk + 8, c, neg_mc, sum);
 }
 
 }  // namespace f2k

@@ -32,6 +32,14 @@ def head_exchange_plan(seq_local: int, n_heads: int, world: int, rank: int) -> d
     }
 
 
+def peer_failures(failed_words, step: int) -> list[int]:
+    """Ranks whose attention kernel gave up during `step`: rank s stores the step number into word
+    s of every peer's "failed" words before it publishes "done" (csrc/headswap.cu), so a rank that
+    sees all "done" words and no marker knows that every row it received was written. Words of
+    earlier steps hold older numbers and do not count. Pure host logic (tested on CPU)."""
+    return [s for s, wd in enumerate(failed_words) if step > 0 and int(wd) == step]
+
+
 class HeadExchangeAttention:
     def __init__(self, seq_local: int, n_heads: int, head_dim: int, world: int, rank: int, scale: float = 0.0):
         self.world, self.rank = world, rank
@@ -114,3 +122,11 @@ class HeadExchangeAttention:
         st = C.c_int(0)
         lib.f2k_hx_device_status(self._h, C.byref(st))
         return st.value
+
+    def set_wait_limits(self, in_cta_clk: int = 0, peer_clk: int = 0) -> bool:
+        """Limits of the kernels' bounded waits in SM clock cycles (0 = default)."""
+        return lib.f2k_hx_set_wait_limits(self._h, in_cta_clk, peer_clk) == _lib.F2K_OK
+
+    def abort(self) -> bool:
+        """Releases the stream waits of output() when a peer never delivered."""
+        return lib.f2k_hx_abort(self._h) == _lib.F2K_OK

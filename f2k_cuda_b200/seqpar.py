@@ -117,6 +117,14 @@ class SequenceParallelAttention:
         lib.f2k_seqpar_device_status(self._h, C.byref(st))
         return st.value
 
+    def set_wait_limits(self, in_cta_clk: int = 0, peer_clk: int = 0) -> bool:
+        """Limits of the kernels' bounded waits in SM clock cycles (0 = default)."""
+        return lib.f2k_seqpar_set_wait_limits(self._h, in_cta_clk, peer_clk) == _lib.F2K_OK
+
+    def abort(self) -> bool:
+        """Releases the copy stream of the current step when a peer never announced its K/V."""
+        return lib.f2k_seqpar_abort(self._h) == _lib.F2K_OK
+
 
 def qk_norm_rope(x, y, gamma, cos_table, sin_table, eps: float, stream=None) -> bool:
     """y = RoPE(RMSNorm(x) * gamma) per head row of x [batch, seq, heads, 128]; position = token

@@ -14,6 +14,11 @@
  *    the same handle.
  *  - forward calls are asynchronous on `stream`, never synchronise and never allocate
  *    (the *_host variant allocates its staging buffers on its first call only).
+ *  - The kernels use 16-byte loads and stores: every tensor, gain and RoPE-table pointer must be
+ *    16-byte aligned, and a call with one that is not is refused with F2K_ERR_INVALID before
+ *    anything is launched. (The reference's stand-alone kernels use 2-byte accesses and take any
+ *    bf16-aligned pointer; its callers only ever pass cudaMalloc'd bases and whole-row offsets,
+ *    which are 16-byte aligned.)
  *  - A handle holds mutable state (error text, cached TMA descriptors): use it from
  *    one host thread at a time. Distinct handles on distinct streams are independent.
  *  - There is no CPU fallback and no other GPU path: on a device that is not
@@ -160,13 +165,19 @@ int f2k_attn_forward_fused_host(f2k_attn* h,
  * forbids device allocations after start-up, a process whose device memory was all handed out
  * at start-up. It
  * needs no handle (f2k_attn_create allocates a status word) and no workspace: both live in a
- * 32 MiB array that is part of the library image on every GPU that loads it. Shapes whose
+ * 32 MiB array inside the library's device image. Shapes whose
  * normalised Q and K copies do not fit (256 + 2*B*(seq_txt+seq_img)*n_heads*128*2 bytes, each
  * tensor rounded up to 256) are refused with F2K_ERR_WORKSPACE and a message.
- * The first call on a device looks the array's device address up; make that call before any
- * stream capture starts. Nothing in the call allocates or frees. All calls on a device share
- * the array: calls whose GPU work may overlap race on it, so keep them on one stream.
- * errbuf (may be NULL) receives a message when the result is not F2K_OK.
+ * The array's 32 MiB are reserved on a GPU when the CUDA runtime loads the module that holds it
+ * into that GPU's context: with the runtime's default lazy loading that is the FIRST call of
+ * this function or of f2k_attn_noalloc_device_status on the device (with
+ * CUDA_MODULE_LOADING=EAGER, context creation). That first call also looks the array's device
+ * address up and loads the kernels. It is the one call that can fail for lack of device memory:
+ * make it at start-up, before device memory is handed out and before any stream capture
+ * (f2k_attn_noalloc_device_status(NULL, NULL, 0) is enough). After it nothing in these two
+ * calls allocates, frees or loads. The memory stays reserved until the process exits.
+ * All calls on a device share the array: calls whose GPU work may overlap race on it, so keep
+ * them on one stream. errbuf (may be NULL) receives a message when the result is not F2K_OK.
  * No counterpart in the reference, whose callers always allocate their own workspace. */
 int f2k_attn_forward_fused_noalloc(const f2k_attn_config* cfg,
                                    const void* q_txt, const void* k_txt, const void* v_txt,
@@ -177,6 +188,23 @@ int f2k_attn_forward_fused_noalloc(const f2k_attn_config* cfg,
                                    const float* cos_img, const float* sin_img,
                                    float eps, void* o_txt, void* o_img, void* stream,
                                    char* errbuf, size_t errbuf_len);
+
+/* The status word of f2k_attn_forward_fused_noalloc on the current device (it lives in the same
+ * built-in array; there is no handle to ask). Synchronises the device, stores the word to
+ * *status_out (may be NULL) and, when it is not zero, clears it and returns F2K_ERR_DEVICE: a
+ * bounded wait inside a kernel expired and the outputs of the allocation-free calls since the
+ * last read must not be used. The word is not cleared by the forward calls, so a failure stays
+ * visible until it is read here. Allocates nothing (first call on a device: see above).
+ * No counterpart in the reference, which never checks for asynchronous kernel failure. */
+int f2k_attn_noalloc_device_status(int* status_out, char* errbuf, size_t errbuf_len);
+
+/* Limits of the bounded waits inside the kernels this handle launches, in SM clock cycles
+ * (about 1.9e9 per second); 0 keeps the default. in_cta_clk bounds waits between the roles of one
+ * thread block (default 2e9); peer_clk bounds waits on words that a copy engine or another GPU
+ * writes (default 4e10; only the sequence-parallel layers have such waits). When a wait runs
+ * out the kernel returns normally and f2k_attn_device_status reports F2K_ERR_DEVICE.
+ * No counterpart in the reference, whose kernels never wait on anything. */
+int f2k_attn_set_wait_limits(f2k_attn* h, long long in_cta_clk, long long peer_clk);
 
 /* Reads and clears the device status word the kernels of this handle write
  * (0 = clean). Synchronises the device. A non-zero word means a bounded wait inside
@@ -246,6 +274,17 @@ int f2k_seqpar_local_kv(f2k_seqpar* h, void** k, void** v);
 int f2k_seqpar_forward(f2k_seqpar* h, const void* q_local, void* o_local, int overlap,
                        void* compute_stream, void* copy_stream);
 int f2k_seqpar_device_status(f2k_seqpar* h, int* status_out);
+/* As f2k_attn_set_wait_limits, for the kernels of this handle. peer_clk bounds the wait for a
+ * remote K/V shard's arrival; it has to cover the skew between the rank processes. */
+int f2k_seqpar_set_wait_limits(f2k_seqpar* h, long long in_cta_clk, long long peer_clk);
+/* The way out when a peer is gone: forward() parks the copy stream on waits for the peers'
+ * "written" words, and with a dead peer neither that stream nor anything that synchronises with
+ * it (f2k_seqpar_device_status, f2k_seqpar_destroy) would ever return. abort writes the awaited
+ * words of the current step itself (on a stream of its own; it does not touch the caller's
+ * streams), so the step drains: the pulls copy whatever the peers' slots hold, the kernel's
+ * bounded waits are satisfied or have expired, and f2k_seqpar_device_status then returns
+ * F2K_ERR_DEVICE once. The output of the aborted step is invalid. */
+int f2k_seqpar_abort(f2k_seqpar* h);
 
 /* ---- sequence-parallel attention by head exchange ----------------------------------------
  * Same sharding outside (rank r holds Q, K, V of its seq_local tokens, all heads, and gets the
@@ -256,7 +295,9 @@ int f2k_seqpar_device_status(f2k_seqpar* h, int* status_out);
  * rank that owns the token (attend). Traffic per GPU and step is 4 * (world-1)/world shards
  * against 2 * (world-1) shards for the ring above. batch must be 1; world must divide n_heads.
  * Uses f2k_seqpar_config; buffers are exported/attached like the ring's. No reference
- * counterpart. Call order per step, all on one stream: exchange_in, attend, output. */
+ * counterpart. Call order per step, all on one stream: exchange_in, attend, output; a call out of
+ * that order is refused (the stream wait of output is what makes the two buffer sets safe to
+ * reuse, so a step may not be left unfinished). */
 typedef struct f2k_hx f2k_hx; /* opaque */
 int         f2k_hx_create(const f2k_seqpar_config* cfg, f2k_hx** out);
 void        f2k_hx_destroy(f2k_hx* h);
@@ -273,7 +314,15 @@ int f2k_hx_attend(f2k_hx* h, void* stream);
  * then this rank's [seq_local, n_heads, 128] bf16 output (inside the exchange buffer; valid
  * until the exchange_in after next). */
 int f2k_hx_output(f2k_hx* h, void** o_local, void* stream);
+/* F2K_ERR_DEVICE when a bounded wait of this rank's kernels expired, when a PEER's attention
+ * kernel gave up during the last step (it marks this rank's control words before it publishes
+ * "done", so stale rows cannot be taken for valid ones), or after f2k_hx_abort. */
 int f2k_hx_device_status(f2k_hx* h, int* status_out);
+int f2k_hx_set_wait_limits(f2k_hx* h, long long in_cta_clk, long long peer_clk);
+/* Releases the stream waits f2k_hx_output queued when a peer is gone (writes this rank's "done"
+ * words of the current step itself, on a stream of its own). The step's output is invalid;
+ * f2k_hx_device_status then returns F2K_ERR_DEVICE once, and the next exchange_in is accepted. */
+int f2k_hx_abort(f2k_hx* h);
 
 /* CUDA IPC for the shard buffers: 64-byte handles to pass between the rank processes. */
 int f2k_ipc_export(const void* base, void* handle64);

@@ -181,13 +181,48 @@ static void prep_rows(int mode, int apply_prologue, const uint16_t* x, const uin
     }
 }
 
+/* One query row against all S keys: two-pass softmax (tests/test_attention.cu:56-86). In the
+ * reference-rounding mode the score is scaled in fp32, the row sum is taken from fp32 P and P
+ * enters P.V as bf16 (attention.cu:699-714). sc: S doubles, acc: D doubles of scratch. */
+static void attend_row(int mode, const double* qr, const double* k, const double* v, int S, int D,
+                       double scale, double* sc, double* acc, float* orow) {
+    const float scale_f = (float)scale;
+    double mx = -1e300;
+    for (int kj = 0; kj < S; ++kj) {
+        const double* kr = k + (size_t)kj * D;
+        double dot = 0.0;
+        for (int d = 0; d < D; ++d) dot += qr[d] * kr[d];
+        double s = (mode == F2K_ORACLE_IDEAL) ? dot * scale : (double)((float)dot * scale_f);
+        sc[kj] = s;
+        if (s > mx) mx = s;
+    }
+    double sum = 0.0;
+    for (int d = 0; d < D; ++d) acc[d] = 0.0;
+    for (int kj = 0; kj < S; ++kj) {
+        double p = exp(sc[kj] - mx);
+        if (mode != F2K_ORACLE_IDEAL) {
+            const float pf = (float)p;
+            sum += pf;               /* row sum from fp32 P */
+            p = BF2F(F2BF(pf));      /* P enters P.V as bf16 */
+        } else {
+            sum += p;
+        }
+        const double* vr = v + (size_t)kj * D;
+        for (int d = 0; d < D; ++d) acc[d] += p * vr[d];
+    }
+    const double inv = 1.0 / sum;
+    for (int d = 0; d < D; ++d) {
+        const float o = (float)(acc[d] * inv);
+        orow[d] = (mode == F2K_ORACLE_IDEAL) ? o : BF2F(F2BF(o));
+    }
+}
+
 int f2k_oracle_joint_path(const f2k_oracle_problem* pr, float* o_txt, float* o_img) {
     const int B = pr->batch, St = pr->seq_txt, Si = pr->seq_img, H = pr->n_heads, D = pr->head_dim;
     const int S = St + Si;
     if (B <= 0 || St < 0 || Si <= 0 || H <= 0 || D <= 0 || (D & 1)) return 1;
     const int h0 = pr->head_begin, h1 = pr->head_end > 0 ? pr->head_end : H;
     const double scale = pr->scale > 0.f ? (double)pr->scale : 1.0 / sqrt((double)D);
-    const float scale_f = (float)scale;
     const int mode = pr->mode;
     int failed = 0;
 
@@ -216,43 +251,59 @@ int f2k_oracle_joint_path(const f2k_oracle_problem* pr, float* o_txt, float* o_i
                     prep_rows(mode, 0, pr->v_img, 0, 0, 0, 0.f, b, h, Si, H, D, v + (size_t)St * D);
 
                     for (int qi = 0; qi < S; ++qi) {
-                        const double* qr = q + (size_t)qi * D;
-                        double mx = -1e300;
-                        for (int kj = 0; kj < S; ++kj) {
-                            const double* kr = k + (size_t)kj * D;
-                            double dot = 0.0;
-                            for (int d = 0; d < D; ++d) dot += qr[d] * kr[d];
-                            double s = (mode == F2K_ORACLE_IDEAL) ? dot * scale
-                                                                 : (double)((float)dot * scale_f);
-                            sc[kj] = s;
-                            if (s > mx) mx = s;
-                        }
-                        double sum = 0.0;
-                        for (int d = 0; d < D; ++d) acc[d] = 0.0;
-                        for (int kj = 0; kj < S; ++kj) {
-                            double p = exp(sc[kj] - mx);
-                            if (mode != F2K_ORACLE_IDEAL) {
-                                const float pf = (float)p;
-                                sum += pf;               /* row sum from fp32 P */
-                                p = BF2F(F2BF(pf));      /* P enters P.V as bf16 */
-                            } else {
-                                sum += p;
-                            }
-                            const double* vr = v + (size_t)kj * D;
-                            for (int d = 0; d < D; ++d) acc[d] += p * vr[d];
-                        }
-                        const double inv = 1.0 / sum;
                         float* orow = qi < St ? o_txt + (((size_t)b * St + qi) * H + h) * D
                                               : o_img + (((size_t)b * Si + (qi - St)) * H + h) * D;
-                        for (int d = 0; d < D; ++d) {
-                            const float o = (float)(acc[d] * inv);
-                            orow[d] = (mode == F2K_ORACLE_IDEAL) ? o : BF2F(F2BF(o));
-                        }
+                        attend_row(mode, q + (size_t)qi * D, k, v, S, D, scale, sc, acc, orow);
                     }
                 }
         }
         free(q); free(k); free(v); free(sc); free(acc);
     }
+    return failed;
+}
+
+/* The same path for SELECTED query rows of ONE (batch, head): rows[i] indexes the joint
+ * text||image sequence, out is [n_rows][D]. The threads share the head's prepared Q, K, V and
+ * split the rows, so that a head subset of the 8704- and 16896-token shapes is checked in
+ * seconds. Arithmetic per row is attend_row, exactly as in f2k_oracle_joint_path. */
+int f2k_oracle_joint_rows(const f2k_oracle_problem* pr, int b, int h, const int* rows, int n_rows, float* out) {
+    const int B = pr->batch, St = pr->seq_txt, Si = pr->seq_img, H = pr->n_heads, D = pr->head_dim;
+    const int S = St + Si;
+    if (B <= 0 || St < 0 || Si <= 0 || H <= 0 || D <= 0 || (D & 1) || b < 0 || b >= B || h < 0 || h >= H || n_rows < 0)
+        return 1;
+    for (int i = 0; i < n_rows; ++i)
+        if (rows[i] < 0 || rows[i] >= S) return 1;
+    const double scale = pr->scale > 0.f ? (double)pr->scale : 1.0 / sqrt((double)D);
+    const int mode = pr->mode;
+    double* q = (double*)malloc(sizeof(double) * (size_t)S * D);
+    double* k = (double*)malloc(sizeof(double) * (size_t)S * D);
+    double* v = (double*)malloc(sizeof(double) * (size_t)S * D);
+    int failed = !q || !k || !v;
+    if (!failed) {
+        if (St > 0) {
+            prep_rows(mode, pr->apply_prologue, pr->q_txt, pr->gamma_q_txt, pr->cos_txt, pr->sin_txt, pr->eps, b, h, St, H, D, q);
+            prep_rows(mode, pr->apply_prologue, pr->k_txt, pr->gamma_k_txt, pr->cos_txt, pr->sin_txt, pr->eps, b, h, St, H, D, k);
+            prep_rows(mode, 0, pr->v_txt, 0, 0, 0, 0.f, b, h, St, H, D, v);
+        }
+        prep_rows(mode, pr->apply_prologue, pr->q_img, pr->gamma_q_img, pr->cos_img, pr->sin_img, pr->eps, b, h, Si, H, D, q + (size_t)St * D);
+        prep_rows(mode, pr->apply_prologue, pr->k_img, pr->gamma_k_img, pr->cos_img, pr->sin_img, pr->eps, b, h, Si, H, D, k + (size_t)St * D);
+        prep_rows(mode, 0, pr->v_img, 0, 0, 0, 0.f, b, h, Si, H, D, v + (size_t)St * D);
+#pragma omp parallel
+        {
+            double* sc = (double*)malloc(sizeof(double) * (size_t)S);
+            double* acc = (double*)malloc(sizeof(double) * (size_t)D);
+            if (!sc || !acc) {
+#pragma omp atomic write
+                failed = 1;
+            } else {
+#pragma omp for schedule(dynamic, 4)
+                for (int i = 0; i < n_rows; ++i)
+                    attend_row(mode, q + (size_t)rows[i] * D, k, v, S, D, scale, sc, acc, out + (size_t)i * D);
+            }
+            free(sc); free(acc);
+        }
+    }
+    free(q); free(k); free(v);
     return failed;
 }
 

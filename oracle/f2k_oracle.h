@@ -29,6 +29,10 @@ typedef struct f2k_oracle_problem {
  * Returns 0 on success. */
 int f2k_oracle_joint_path(const f2k_oracle_problem* pr, float* o_txt, float* o_img);
 
+/* Selected query rows (indices into the joint text||image sequence) of one (batch, head):
+ * out is fp32 [n_rows][D]. Same arithmetic as f2k_oracle_joint_path; threads split the rows. */
+int f2k_oracle_joint_rows(const f2k_oracle_problem* pr, int b, int h, const int* rows, int n_rows, float* out);
+
 int f2k_oracle_attention_f32(const uint16_t* Q, const uint16_t* K, const uint16_t* V, float* O,
                              int B, int S, int H, int D, float scale, int head_begin, int head_end);
 

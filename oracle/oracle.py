@@ -22,9 +22,9 @@ IDEAL, REF_ROUND = 0, 1
 
 
 def build(ref: bool = True) -> None:
-    """(Re)build the checker libraries; `ref` also rebuilds oracle/_ref when the
-    reference checkout is present."""
-    subprocess.run(["make", "-C", str(HERE), "oracle"] + (["ref"] if ref else []),
+    """(Re)build the checker libraries; `ref` also rebuilds oracle/_ref (the reference's attention
+    path and the block-level test programs) when the reference checkout is present."""
+    subprocess.run(["make", "-C", str(HERE), "oracle"] + (["ref", "blocks"] if ref else []),
                    check=True, capture_output=True)
 
 
@@ -75,6 +75,8 @@ class Oracle:
         L = self.lib
         L.f2k_oracle_joint_path.restype = C.c_int
         L.f2k_oracle_joint_path.argtypes = [C.POINTER(_Problem), C.c_void_p, C.c_void_p]
+        L.f2k_oracle_joint_rows.restype = C.c_int
+        L.f2k_oracle_joint_rows.argtypes = [C.POINTER(_Problem), C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_void_p]
         L.f2k_oracle_attention_f32.restype = C.c_int
         L.f2k_oracle_attention_f32.argtypes = [C.c_void_p] * 4 + [C.c_int] * 4 + [C.c_float, C.c_int, C.c_int]
         L.f2k_oracle_rmsnorm_ideal.argtypes = [C.c_void_p] * 3 + [C.c_long, C.c_int, C.c_float]
@@ -87,6 +89,42 @@ class Oracle:
     @property
     def threads(self) -> int:
         return int(self.lib.f2k_oracle_num_threads())
+
+    def _problem(self, q_img, k_img, v_img, q_txt, k_txt, v_txt, gammas, tables, eps, scale, mode):
+        q_img, k_img, v_img = _u16(q_img), _u16(k_img), _u16(v_img)
+        B, Si, H, D = q_img.shape
+        St = 0 if q_txt is None else q_txt.shape[1]
+        q_txt, k_txt, v_txt = _u16(q_txt), _u16(k_txt), _u16(v_txt)
+        pro = gammas is not None
+        keep = [q_img, k_img, v_img, q_txt, k_txt, v_txt]
+        pr = _Problem()
+        pr.mode, pr.apply_prologue = mode, int(pro)
+        pr.batch, pr.seq_txt, pr.seq_img, pr.n_heads, pr.head_dim = B, St, Si, H, D
+        pr.head_begin, pr.head_end = 0, H
+        pr.scale, pr.eps = scale, eps
+        pr.q_txt, pr.k_txt, pr.v_txt = _ptr(q_txt), _ptr(k_txt), _ptr(v_txt)
+        pr.q_img, pr.k_img, pr.v_img = _ptr(q_img), _ptr(k_img), _ptr(v_img)
+        if pro:
+            g = [_u16(x) for x in gammas]
+            t = [_f32(x) for x in tables]
+            keep += g + t
+            pr.gamma_q_txt, pr.gamma_k_txt, pr.gamma_q_img, pr.gamma_k_img = map(_ptr, g)
+            pr.cos_txt, pr.sin_txt, pr.cos_img, pr.sin_img = map(_ptr, t)
+        return pr, keep
+
+    def joint_rows(self, rows, *, batch=0, head=0, q_img, k_img, v_img, q_txt=None, k_txt=None, v_txt=None,
+                   gammas=None, tables=None, eps=1e-6, scale=0.0, mode=IDEAL):
+        """The joint path for selected query rows (indices into the text||image sequence) of one
+        (batch, head): float32 [len(rows), D]. All threads work on the one head, so long
+        sequences are checked in seconds."""
+        pr, keep = self._problem(q_img, k_img, v_img, q_txt, k_txt, v_txt, gammas, tables, eps, scale, mode)
+        rows = np.ascontiguousarray(rows, dtype=np.int32)
+        out = np.zeros((len(rows), pr.head_dim), np.float32)
+        rc = self.lib.f2k_oracle_joint_rows(C.byref(pr), batch, head, _ptr(rows), len(rows), _ptr(out))
+        if rc != 0:
+            raise RuntimeError("oracle: bad problem, bad row index or out of memory")
+        del keep
+        return out
 
     def joint_path(self, *, q_img, k_img, v_img, q_txt=None, k_txt=None, v_txt=None,
                    gammas=None, tables=None, eps=1e-6, scale=0.0, mode=IDEAL,

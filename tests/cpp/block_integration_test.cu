@@ -1,0 +1,211 @@
+// Block-level integration check: the reference's UNMODIFIED DoubleStreamBlock and
+// SingleStreamBlock (F2K_CUDA src/backend/cuda/double_stream_block.cu, single_stream_block.cu,
+// compiled from the reference checkout where they lie, with its layernorm / modulation / silu /
+// split kernels) driven on synthetic activations, with a stub Linear (stub_linear.cu) in place of
+// the CUTLASS GEMMs.
+//
+// The program is built twice by oracle/Makefile (target `blocks`):
+//   block_test_ours  the blocks see this repository's csrc/compat headers and link libf2k_attn.so:
+//                    their rmsnorm_bf16 / rope_4axis_inplace_bf16 / JointAttention / Attention
+//                    calls land in the sm_100a kernels;
+//   block_test_ref   the same sources against the reference's own attention path.
+// Each run makes the checks of the reference's block tests (tests/test_double_stream_block.cu:
+// 116-259, tests/test_single_stream_block.cu:192-200): with all modulation vectors zero the block
+// is the identity (max error < 0.02, mean < 0.001), and with gates around 0.2 the output is finite,
+// bounded and not degenerate. With a path as argument it also writes the four output tensors of the
+// gated runs, so that the two builds can be compared (tests/test_cpp_surface_gpu.py).
+#include "backend/cuda/double_stream_block.h"
+#include "backend/cuda/single_stream_block.h"
+#include "backend/cuda/kernels/rope_4axis.h"
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <vector>
+
+namespace {
+
+uint16_t to_bf16(float f) {
+    uint32_t u;
+    std::memcpy(&u, &f, 4);
+    u += 0x7FFFu + ((u >> 16) & 1u);
+    return (uint16_t)(u >> 16);
+}
+float from_bf16(uint16_t b) {
+    uint32_t u = (uint32_t)b << 16;
+    float f;
+    std::memcpy(&f, &u, 4);
+    return f;
+}
+struct Rng {
+    uint64_t s;
+    float uniform(float lo, float hi) {
+        s = s * 6364136223846793005ull + 1442695040888963407ull;
+        return lo + (hi - lo) * ((float)((s >> 40) & 0xFFFFFF) / 16777216.0f);
+    }
+};
+std::vector<uint16_t> fill(Rng& r, size_t n, float lo, float hi) {
+    std::vector<uint16_t> v(n);
+    for (auto& x : v) x = to_bf16(r.uniform(lo, hi));
+    return v;
+}
+void* upload(const void* h, size_t bytes) {
+    void* d = nullptr;
+    if (cudaMalloc(&d, bytes) != cudaSuccess) return nullptr;
+    cudaMemcpy(d, h, bytes, cudaMemcpyHostToDevice);
+    return d;
+}
+struct Stats { int bad = 0; double max_abs = 0, mean_abs = 0, max_diff = 0, mean_diff = 0; };
+Stats stats(const std::vector<uint16_t>& out, const std::vector<uint16_t>& in) {
+    Stats s;
+    for (size_t i = 0; i < out.size(); ++i) {
+        const float o = from_bf16(out[i]), x = from_bf16(in[i]);
+        if (!std::isfinite(o)) ++s.bad;
+        s.max_abs = std::fmax(s.max_abs, std::fabs(o));
+        s.mean_abs += std::fabs(o);
+        s.max_diff = std::fmax(s.max_diff, std::fabs(o - x));
+        s.mean_diff += std::fabs(o - x);
+    }
+    s.mean_abs /= out.size();
+    s.mean_diff /= out.size();
+    return s;
+}
+
+// RoPE tables with the transformer's layout (flux_transformer.cu:288-319): text (0,0,0,l), image
+// (0, s / W, s % W, 0), through the module's own host builder.
+void tables(int seq_txt, int grid_w, int seq_img, std::vector<float>& cos_t, std::vector<float>& sin_t,
+            std::vector<float>& cos_i, std::vector<float>& sin_i, std::vector<float>& cos_c, std::vector<float>& sin_c) {
+    std::vector<std::vector<int>> pt(seq_txt, std::vector<int>(4, 0)), pi(seq_img, std::vector<int>(4, 0));
+    for (int l = 0; l < seq_txt; ++l) pt[l][3] = l;
+    for (int s = 0; s < seq_img; ++s) { pi[s][1] = s / grid_w; pi[s][2] = s % grid_w; }
+    const std::vector<int> axes{32, 32, 32, 32};
+    f2k::cuda::build_rope_4axis_tables(axes, pt, 2000.0f, cos_t, sin_t);
+    f2k::cuda::build_rope_4axis_tables(axes, pi, 2000.0f, cos_i, sin_i);
+    cos_c = cos_t; cos_c.insert(cos_c.end(), cos_i.begin(), cos_i.end());
+    sin_c = sin_t; sin_c.insert(sin_c.end(), sin_i.begin(), sin_i.end());
+}
+
+constexpr int B = 1, S_TXT = 128, GRID_W = 16, S_IMG = 256, H = 4, D = 128;
+constexpr int HIDDEN = H * D, FFN = 3 * HIDDEN;
+
+bool run_double(bool zero_gate, FILE* dump) {
+    Rng rng{zero_gate ? 0xD0B1Eull : 0xD0B1Full};
+    f2k::cuda::PreQuantNVFP4 w{};        // the stub Linear never reads weights; the blocks only check for non-null
+    auto nq = fill(rng, D, 0.9f, 1.1f), nk = fill(rng, D, 0.9f, 1.1f), naq = fill(rng, D, 0.9f, 1.1f), nak = fill(rng, D, 0.9f, 1.1f);
+    f2k::cuda::DoubleStreamBlock::Config cfg;
+    cfg.batch = B; cfg.seq_img = S_IMG; cfg.seq_txt = S_TXT; cfg.n_heads = H; cfg.head_dim = D; cfg.ffn_dim = FFN;
+    cfg.W_q = cfg.W_k = cfg.W_v = cfg.W_out = cfg.W_ff_in = cfg.W_ff_out = &w;
+    cfg.W_add_q = cfg.W_add_k = cfg.W_add_v = cfg.W_add_out = cfg.W_ff_ctx_in = cfg.W_ff_ctx_out = &w;
+    cfg.norm_q_bf16 = nq.data(); cfg.norm_k_bf16 = nk.data();
+    cfg.norm_added_q_bf16 = naq.data(); cfg.norm_added_k_bf16 = nak.data();
+    f2k::cuda::DoubleStreamBlock blk(cfg);
+    if (!blk.ok()) { std::printf("FAIL DoubleStreamBlock ctor: %s\n", blk.last_error()); return false; }
+
+    void* mod[12];
+    for (int i = 0; i < 12; ++i) {
+        const bool gate = i % 3 == 2;      // order below: scale, shift, gate per (stream, half)
+        auto v = zero_gate ? std::vector<uint16_t>(HIDDEN, to_bf16(0.f))
+                           : fill(rng, HIDDEN, gate ? 0.1f : -0.1f, gate ? 0.3f : 0.1f);
+        mod[i] = upload(v.data(), v.size() * 2);
+    }
+    f2k::cuda::DoubleStreamBlock::Modulation m;
+    m.img_scale_attn = mod[0]; m.img_shift_attn = mod[1]; m.img_gate_attn = mod[2];
+    m.img_scale_mlp  = mod[3]; m.img_shift_mlp  = mod[4]; m.img_gate_mlp  = mod[5];
+    m.txt_scale_attn = mod[6]; m.txt_shift_attn = mod[7]; m.txt_gate_attn = mod[8];
+    m.txt_scale_mlp  = mod[9]; m.txt_shift_mlp  = mod[10]; m.txt_gate_mlp = mod[11];
+
+    auto himg = fill(rng, (size_t)B * S_IMG * HIDDEN, -1.f, 1.f), htxt = fill(rng, (size_t)B * S_TXT * HIDDEN, -1.f, 1.f);
+    std::vector<float> ct, st, ci, si, cc, sc;
+    tables(S_TXT, GRID_W, S_IMG, ct, st, ci, si, cc, sc);
+    void* d_img = upload(himg.data(), himg.size() * 2);
+    void* d_txt = upload(htxt.data(), htxt.size() * 2);
+    float* d_ct = (float*)upload(ct.data(), ct.size() * 4); float* d_st = (float*)upload(st.data(), st.size() * 4);
+    float* d_ci = (float*)upload(ci.data(), ci.size() * 4); float* d_si = (float*)upload(si.data(), si.size() * 4);
+    void* d_ws = nullptr;
+    cudaMalloc(&d_ws, blk.workspace_size_bytes());
+    const bool ok = blk.forward(d_img, d_txt, m, d_ci, d_si, d_ct, d_st, d_ws, blk.workspace_size_bytes());
+    const cudaError_t e = cudaDeviceSynchronize();
+    std::vector<uint16_t> oimg(himg.size()), otxt(htxt.size());
+    cudaMemcpy(oimg.data(), d_img, oimg.size() * 2, cudaMemcpyDeviceToHost);
+    cudaMemcpy(otxt.data(), d_txt, otxt.size() * 2, cudaMemcpyDeviceToHost);
+    for (void* p : mod) cudaFree(p);
+    cudaFree(d_img); cudaFree(d_txt); cudaFree(d_ct); cudaFree(d_st); cudaFree(d_ci); cudaFree(d_si); cudaFree(d_ws);
+    if (!ok || e != cudaSuccess) { std::printf("FAIL DoubleStreamBlock forward: %s / %s\n", blk.last_error(), cudaGetErrorString(e)); return false; }
+    const Stats a = stats(oimg, himg), t = stats(otxt, htxt);
+    bool pass;
+    if (zero_gate) {
+        pass = a.max_diff < 0.02 && a.mean_diff < 0.001 && t.max_diff < 0.02 && t.mean_diff < 0.001;
+        std::printf("%s DoubleStreamBlock zero-gate identity: img[max=%.5f mean=%.6f] txt[max=%.5f mean=%.6f]\n",
+                    pass ? "PASS" : "FAIL", a.max_diff, a.mean_diff, t.max_diff, t.mean_diff);
+    } else {
+        pass = a.bad + t.bad == 0 && a.max_abs < 500 && t.max_abs < 500 && a.mean_abs > 0.05 && t.mean_abs > 0.05 &&
+               a.mean_diff > 1e-3 && t.mean_diff > 1e-3;       // and the block did something
+        std::printf("%s DoubleStreamBlock gated: img[bad=%d max=%.3f mean=%.3f moved=%.4f] txt[bad=%d max=%.3f mean=%.3f moved=%.4f]\n",
+                    pass ? "PASS" : "FAIL", a.bad, a.max_abs, a.mean_abs, a.mean_diff, t.bad, t.max_abs, t.mean_abs, t.mean_diff);
+        if (dump) { std::fwrite(oimg.data(), 2, oimg.size(), dump); std::fwrite(otxt.data(), 2, otxt.size(), dump); }
+    }
+    return pass;
+}
+
+bool run_single(bool zero_gate, FILE* dump) {
+    Rng rng{zero_gate ? 0x51261Eull : 0x51261Full};
+    const int S = S_TXT + S_IMG;
+    f2k::cuda::PreQuantNVFP4 w{};
+    auto nq = fill(rng, D, 0.9f, 1.1f), nk = fill(rng, D, 0.9f, 1.1f);
+    f2k::cuda::SingleStreamBlock::Config cfg;
+    cfg.batch = B; cfg.seq = S; cfg.n_heads = H; cfg.head_dim = D; cfg.ffn_dim = FFN;
+    cfg.W_qkv_mlp_proj = &w; cfg.W_out = &w; cfg.norm_q_bf16 = nq.data(); cfg.norm_k_bf16 = nk.data();
+    f2k::cuda::SingleStreamBlock blk(cfg);
+    if (!blk.ok()) { std::printf("FAIL SingleStreamBlock ctor: %s\n", blk.last_error()); return false; }
+    void* mod[3];
+    for (int i = 0; i < 3; ++i) {
+        auto v = zero_gate ? std::vector<uint16_t>(HIDDEN, to_bf16(0.f))
+                           : fill(rng, HIDDEN, i == 2 ? 0.1f : -0.1f, i == 2 ? 0.3f : 0.1f);
+        mod[i] = upload(v.data(), v.size() * 2);
+    }
+    f2k::cuda::SingleStreamBlock::Modulation m;
+    m.scale = mod[0]; m.shift = mod[1]; m.gate = mod[2];
+    auto hx = fill(rng, (size_t)B * S * HIDDEN, -1.f, 1.f);
+    std::vector<float> ct, st, ci, si, cc, sc;
+    tables(S_TXT, GRID_W, S_IMG, ct, st, ci, si, cc, sc);
+    void* d_x = upload(hx.data(), hx.size() * 2);
+    float* d_c = (float*)upload(cc.data(), cc.size() * 4); float* d_s = (float*)upload(sc.data(), sc.size() * 4);
+    void* d_ws = nullptr;
+    cudaMalloc(&d_ws, blk.workspace_size_bytes());
+    const bool ok = blk.forward(d_x, m, d_c, d_s, d_ws, blk.workspace_size_bytes());
+    const cudaError_t e = cudaDeviceSynchronize();
+    std::vector<uint16_t> ox(hx.size());
+    cudaMemcpy(ox.data(), d_x, ox.size() * 2, cudaMemcpyDeviceToHost);
+    for (void* p : mod) cudaFree(p);
+    cudaFree(d_x); cudaFree(d_c); cudaFree(d_s); cudaFree(d_ws);
+    if (!ok || e != cudaSuccess) { std::printf("FAIL SingleStreamBlock forward: %s / %s\n", blk.last_error(), cudaGetErrorString(e)); return false; }
+    const Stats a = stats(ox, hx);
+    bool pass;
+    if (zero_gate) {
+        pass = a.max_diff < 0.02 && a.mean_diff < 0.001;
+        std::printf("%s SingleStreamBlock zero-gate identity: max=%.5f mean=%.6f\n", pass ? "PASS" : "FAIL", a.max_diff, a.mean_diff);
+    } else {
+        pass = a.bad == 0 && a.max_abs < 200 && a.mean_abs > 0.05 && a.mean_diff > 1e-3;
+        std::printf("%s SingleStreamBlock gated: bad=%d max=%.3f mean=%.3f moved=%.4f\n", pass ? "PASS" : "FAIL", a.bad,
+                    a.max_abs, a.mean_abs, a.mean_diff);
+        if (dump) std::fwrite(ox.data(), 2, ox.size(), dump);
+    }
+    return pass;
+}
+
+}  // namespace
+
+int main(int argc, char** argv) {
+    FILE* dump = argc > 1 ? std::fopen(argv[1], "wb") : nullptr;
+    bool ok = true;
+    ok &= run_double(true, nullptr);
+    ok &= run_double(false, dump);
+    ok &= run_single(true, nullptr);
+    ok &= run_single(false, dump);
+    if (dump) std::fclose(dump);
+    return ok ? 0 : 1;
+}

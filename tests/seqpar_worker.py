@@ -27,6 +27,8 @@ def main():
     assert sp.ok(), sp.last_error()
     assert sp.attach_distributed(), sp.last_error()
     dq = dev_bf16(q[:, b:e])
+    _, ref = oracle.load_oracle().joint_path(q_img=q, k_img=k, v_img=v)   # before the steps: no skew between them
+    dist.barrier()
     # (overlap, head groups a slot is pulled in; 0 = the library's choice)
     for step, (overlap, groups) in enumerate(((True, 0), (False, 0), (True, 2), (True, 0), (True, 4))):
         if groups:
@@ -40,8 +42,6 @@ def main():
         assert sp.forward(dq, do, overlap=overlap), sp.last_error()
         torch.cuda.synchronize()
         assert sp.device_status() == 0, sp.last_error()
-        if step == 0:
-            _, ref = oracle.load_oracle().joint_path(q_img=q, k_img=k, v_img=v)
         assert_parity(host_f32(do), ref[:, b:e], f"rank {rank} step {step}")
     dist.barrier()
     if rank == 0:

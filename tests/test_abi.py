@@ -69,6 +69,38 @@ def test_kernel_wrappers_refuse_like_the_reference():
     assert lib.f2k_rope_4axis_inplace_bf16(one, one, one, one, 0, 128, 8, None) == F2K_ERR_INVALID
 
 
+def test_misaligned_pointers_are_refused_on_the_host():
+    """The kernels use 16-byte loads and stores, so a pointer that is not 16-byte aligned would be
+    a misaligned-address fault on the GPU. Every entry point that takes no handle refuses it before
+    it touches CUDA at all (so this runs without a GPU); the handle-based ones are covered by the
+    GPU tests. Nothing is launched by any call here."""
+    from f2k_cuda_b200._lib import AttnConfig, F2K_ERR_INVALID, lib
+    ok, odd, four = C.c_void_p(256), C.c_void_p(258), C.c_void_p(260)
+    for bad in range(3):     # x, gamma, y
+        args = [ok, ok, ok]
+        args[bad] = odd
+        assert lib.f2k_rmsnorm_bf16(*args, 4, 128, 1e-6, None) == F2K_ERR_INVALID
+    for bad in range(3):     # x, cos, sin at head_dim 128
+        args = [ok, ok, ok]
+        args[bad] = four
+        assert lib.f2k_rope_4axis_inplace_bf16(*args, ok, 4, 128, 8, None) == F2K_ERR_INVALID
+    # other head dims read x four bytes at a time and the tables one float at a time
+    assert lib.f2k_rope_4axis_inplace_bf16(odd, ok, ok, ok, 4, 64, 8, None) == F2K_ERR_INVALID
+    assert lib.f2k_rope_4axis_inplace_bf16(ok, odd, ok, ok, 4, 64, 8, None) == F2K_ERR_INVALID
+    assert lib.f2k_rope_4axis_inplace_bf16(ok, ok, ok, odd, 4, 64, 8, None) == F2K_ERR_INVALID
+    for bad in range(5):     # x, y, gamma, cos, sin
+        args = [ok] * 5
+        args[bad] = odd
+        assert lib.f2k_qk_norm_rope_bf16(*args, 1, 8, 4, 1e-6, None) == F2K_ERR_INVALID
+    err = C.create_string_buffer(256)
+    cfg = AttnConfig(1, 8, 64, 4, 128, 0.0)
+    for bad in range(16):    # q, k, v per stream, four gains, four tables, two outputs
+        args = [ok] * 16
+        args[bad] = odd
+        rc = lib.f2k_attn_forward_fused_noalloc(C.byref(cfg), *args[:14], 1e-6, args[14], args[15], None, err, len(err))
+        assert rc == F2K_ERR_INVALID and b"16-byte aligned" in err.value, (bad, err.value)
+
+
 def test_table_builder_matches_oracle_and_reference_golden(orc):
     import f2k_cuda_b200 as f
     g = np.load(ROOT / "tests" / "golden" / "rope_tables.npz")

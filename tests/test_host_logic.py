@@ -191,7 +191,20 @@ def _head_exchange_worker(rank, world, port, out):
             (c0, c1), rows = everyone[src][rank]
             o[:, :, c0:c1] = rows
         _, full = orc.joint_path(q_img=q, k_img=k, v_img=v)
-        out[rank] = float(np.max(np.abs(o - full[:, mine])))
+        err = float(np.max(np.abs(o - full[:, mine])))
+        # a second step in which rank 0's "kernel" gives up: it sends no rows back, and marks the
+        # step number in everybody's failed words before "done". Every rank must find the marker.
+        from f2k_cuda_b200.headswap import peer_failures
+        step = 2
+        failed_words = [1] * world                      # what the (clean) first step could have left: older numbers
+        note = {"done": step, "failed": step if rank == 0 else None}
+        everyone = [None] * world
+        dist.all_gather_object(everyone, note)
+        for src in range(world):
+            assert everyone[src]["done"] == step         # "done" always arrives: nobody hangs
+            if everyone[src]["failed"] is not None:
+                failed_words[src] = everyone[src]["failed"]
+        out[rank] = (err, peer_failures(failed_words, step), peer_failures(failed_words, step + 1))
     finally:
         dist.destroy_process_group()
 
@@ -209,7 +222,9 @@ def test_head_exchange_with_two_gloo_ranks():
     for p in procs:
         p.join(180)
         assert p.exitcode == 0
-    assert all(out[r] == 0.0 for r in range(world)), dict(out)   # same arithmetic per head: identical
+    assert all(out[r][0] == 0.0 for r in range(world)), dict(out)   # same arithmetic per head: identical
+    # the failed step is seen by both ranks, as rank 0's, and only for that step
+    assert all(out[r][1] == [0] and out[r][2] == [] for r in range(world)), dict(out)
 
 
 def test_head_exchange_plan_covers_every_head_once():

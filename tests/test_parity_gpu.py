@@ -330,10 +330,11 @@ def test_host_buffer_entry_point(f2k, orc, monkeypatch, batch, heads, mode):
 
 
 @pytest.mark.parametrize("batch,seq_txt,heads", [(1, 0, 8), (2, 64, 4)])
-def test_strided_rows_read_the_projection_output_in_place(f2k, batch, seq_txt, heads):
+def test_strided_rows_read_the_projection_output_in_place(f2k, orc, batch, seq_txt, heads):
     """Q, K, V as column slices of one wide projection buffer (the reference's fused QKV+MLP
-    output, which it first splits) and O as a column slice of the [attn | mlp] buffer: same bits as
-    the dense call on contiguous copies, and nothing outside the O columns is written."""
+    output, which it first splits) and O as a column slice of the [attn | mlp] buffer: inside the
+    gate against the ideal oracle, same bits as the dense call on contiguous copies, and nothing
+    outside the O columns is written."""
     import torch
     from f2k_cuda_b200.inputs import Workload, make_problem
     w = Workload("strided", batch, seq_txt, ((16, 24),), seed=0x57D1)
@@ -377,6 +378,12 @@ def test_strided_rows_read_the_projection_output_in_place(f2k, batch, seq_txt, h
     r_t = torch.empty_like(dt[0]) if seq_txt else None
     assert ja.forward_fused(*dt, *di, g, t, 1e-6, r_t, r_i, ws), ja.last_error()
     torch.cuda.synchronize()
+    kw = dict(q_txt=p.q_txt, k_txt=p.k_txt, v_txt=p.v_txt) if seq_txt else {}
+    ideal_t, ideal_i = orc.joint_path(q_img=p.q_img, k_img=p.k_img, v_img=p.v_img, gammas=p.gammas, tables=tabs,
+                                      eps=1e-6, **kw)
+    assert_parity(host_f32(o_i.contiguous()), ideal_i, "strided rows img vs ideal oracle")
+    if seq_txt:
+        assert_parity(host_f32(o_t.contiguous()), ideal_t, "strided rows txt vs ideal oracle")
     assert torch.equal(o_i, r_i)
     assert bool((out_i[:, :8] == -3.0).all()) and bool((out_i[:, 8 + hd:] == -3.0).all())
     if seq_txt:
