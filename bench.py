@@ -306,7 +306,7 @@ def run_ours(args, rank, world):
     if ja.device_status() != 0:
         raise RuntimeError("attention kernel reported a device-side error during warm-up")
 
-    sampler = ClockSampler(dev) if rank == 0 else None
+    sampler = ClockSampler(dev, period_s=0.001) if rank == 0 else None
     if world > 1:
         torch.distributed.barrier()
     ms = time_region(step, args.steps, stream)
@@ -330,6 +330,7 @@ def run_ours(args, rank, world):
     for _ in range(3):
         attn_only()
     ms_attn = time_region(attn_only, args.steps, stream)
+    clocks = sampler.stop() if sampler else None      # the two headline regions: fused step, kernel alone
 
     # ---- the same fused step back to back for seconds: the chip reaches its power state, the
     # clock samples are many, and the figure is set against the sustained cuBLAS peak
@@ -369,12 +370,14 @@ def run_ours(args, rank, world):
         if world > 1:
             torch.distributed.barrier()
         e2e_steps = max(3, min(args.steps, 20))
+        e2e_sampler = ClockSampler(dev) if rank == 0 else None
         ms_e2e = time_region(step_host, e2e_steps, stream)
+        if clocks is not None:
+            clocks["e2e_region"] = e2e_sampler.stop()
         if world > 1:
             t = torch.tensor([ms_e2e], device="cuda", dtype=torch.float64)
             torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
             ms_e2e = float(t.item())
-    clocks = sampler.stop() if sampler else None
     status = ja.device_status()
     if status != 0:
         raise RuntimeError("attention kernel reported a device-side error")

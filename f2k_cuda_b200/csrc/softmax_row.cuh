@@ -15,23 +15,31 @@
 
 namespace f2k {
 
-// Running maxima of 64 scores folded into 8 independent chains (3-input max, two new scores per
-// step and chain); `first` starts the chains.
+// Running maxima of 64 scores folded into kMaxChains independent chains (3-input max, two new
+// scores per step and chain); `first` starts the chains.
+#ifndef F2K_OPT_MAX_CHAINS
+#define F2K_OPT_MAX_CHAINS 8
+#endif
+constexpr int kMaxChains = F2K_OPT_MAX_CHAINS;   // 8 or 4
 template <bool kFirst>
-__device__ __forceinline__ void row_max64(const uint32_t* s, float (&m)[8]) {
+__device__ __forceinline__ void row_max64(const uint32_t* s, float (&m)[kMaxChains]) {
     using namespace f2k::ptx;
 #pragma unroll
-    for (int i = 0; i < 64; i += 16)
+    for (int i = 0; i < 64; i += 2 * kMaxChains)
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
+        for (int k = 0; k < kMaxChains; ++k) {
             const float a = __uint_as_float(s[i + 2 * k]), b = __uint_as_float(s[i + 2 * k + 1]);
             m[k] = (kFirst && i == 0) ? fmaxf(a, b) : fmax3(m[k], a, b);
         }
 }
-__device__ __forceinline__ float row_max_finish(const float (&m)[8]) {
+__device__ __forceinline__ float row_max_finish(const float (&m)[kMaxChains]) {
     using namespace f2k::ptx;
-    return fmaxf(fmax3(m[0], m[1], m[2]), fmax3(fmax3(m[3], m[4], m[5]), m[6], m[7]));
+    if constexpr (kMaxChains == 8)
+        return fmaxf(fmax3(m[0], m[1], m[2]), fmax3(fmax3(m[3], m[4], m[5]), m[6], m[7]));
+    else
+        return fmaxf(fmax3(m[0], m[1], m[2]), m[3]);
 }
+
 // 2^x for a pair on the FMA pipe. x = n + f by the 1.5*2^23 rounding trick, cubic fit of 2^f on
 // [-0.5, 0.5], exponent patched in with an integer shift-add. x is clamped at -126 so that the
 // exponent arithmetic cannot wrap (the result is then ~2^-126, i.e. nothing).
@@ -51,6 +59,22 @@ __device__ __forceinline__ void exp2_fma_pair(float& r0, float& r1, float x0, fl
     r1 = __uint_as_float((__float_as_uint(t1) << 23) + __float_as_uint(p1));
 }
 
+// The same for one argument with scalar instructions (six FMA-pipe operations, one clamp and one
+// shift-add on the integer pipe).
+__device__ __forceinline__ float exp2_fma_scalar(float x) {
+    constexpr float kMagic = 12582912.0f;  // 1.5 * 2^23
+    x = fmaxf(x, -126.0f);
+    const float t = __fadd_rn(x, kMagic);
+    const float f = __fsub_rn(x, __fsub_rn(t, kMagic));
+    float p = __fmaf_rn(f, 0.0550886838f, 0.242604051f);
+    p = __fmaf_rn(p, f, 0.693276242f);
+    p = __fmaf_rn(p, f, 0.99992894f);
+    return __uint_as_float((__float_as_uint(t) << 23) + __float_as_uint(p));
+}
+#ifndef F2K_OPT_POLY_SCALAR
+#define F2K_OPT_POLY_SCALAR 0
+#endif
+
 // 16 scores -> 8 packed bf16 pairs. `pair0` is the index of the first pair inside its group of 8
 // pairs (0 or 8 key pairs into a 32-key chunk), which decides who takes the polynomial.
 template <int kPolyOf8>
@@ -68,10 +92,17 @@ __device__ __forceinline__ void exp_chunk16(const uint32_t* s, uint32_t* pk, flo
         const bool poly_a = ((pa + 1) * kPolyOf8 / 8) != (pa * kPolyOf8 / 8);
         const bool poly_b = ((pb + 1) * kPolyOf8 / 8) != (pb * kPolyOf8 / 8);
         float p0, p1, p2, p3;
+#if F2K_OPT_POLY_SCALAR
+        if (poly_a) { p0 = exp2_fma_scalar(x0); p1 = exp2_fma_scalar(x1); }
+        else { p0 = ex2_approx(x0); p1 = ex2_approx(x1); }
+        if (poly_b) { p2 = exp2_fma_scalar(x2); p3 = exp2_fma_scalar(x3); }
+        else { p2 = ex2_approx(x2); p3 = ex2_approx(x3); }
+#else
         if (poly_a) exp2_fma_pair(p0, p1, x0, x1);
         else { p0 = ex2_approx(x0); p1 = ex2_approx(x1); }
         if (poly_b) exp2_fma_pair(p2, p3, x2, x3);
         else { p2 = ex2_approx(x2); p3 = ex2_approx(x3); }
+#endif
         add2(sum[0], sum[1], sum[0], sum[1], p0, p1);
         add2(sum[2], sum[3], sum[2], sum[3], p2, p3);
         pk[i / 2 + 0] = pack_bf16x2(p0, p1);

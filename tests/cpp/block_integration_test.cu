@@ -154,11 +154,14 @@ bool run_double(bool zero_gate, FILE* dump) {
 bool run_single(bool zero_gate, FILE* dump) {
     Rng rng{zero_gate ? 0x51261Eull : 0x51261Full};
     const int S = S_TXT + S_IMG;
-    f2k::cuda::PreQuantNVFP4 w{};
+    // the block checks the shapes of its two fused weights; the stub Linear never reads their bits
+    f2k::cuda::PreQuantNVFP4 w_in{}, w_out{};
+    w_in.N = 3 * HIDDEN + 2 * FFN; w_in.K = HIDDEN;
+    w_out.N = HIDDEN; w_out.K = HIDDEN + FFN;
     auto nq = fill(rng, D, 0.9f, 1.1f), nk = fill(rng, D, 0.9f, 1.1f);
     f2k::cuda::SingleStreamBlock::Config cfg;
     cfg.batch = B; cfg.seq = S; cfg.n_heads = H; cfg.head_dim = D; cfg.ffn_dim = FFN;
-    cfg.W_qkv_mlp_proj = &w; cfg.W_out = &w; cfg.norm_q_bf16 = nq.data(); cfg.norm_k_bf16 = nk.data();
+    cfg.W_qkv_mlp_proj = &w_in; cfg.W_out = &w_out; cfg.norm_q_bf16 = nq.data(); cfg.norm_k_bf16 = nk.data();
     f2k::cuda::SingleStreamBlock blk(cfg);
     if (!blk.ok()) { std::printf("FAIL SingleStreamBlock ctor: %s\n", blk.last_error()); return false; }
     void* mod[3];
