@@ -43,10 +43,24 @@ def _stale() -> bool:
 
 
 def build(force: bool = False, verbose: bool = False) -> Path:
-    """Compile the library if it is missing or older than its sources; return its path."""
+    """Compile the library if it is missing or older than its sources; return its path.
+    Safe to call from several processes at once (the ranks of a multi-GPU job all import the
+    package): one builds under a file lock, the others wait and find the library fresh."""
     if not force and not _stale():
         return LIB_PATH
     BUILD_DIR.mkdir(exist_ok=True)
+    import fcntl
+    with open(BUILD_DIR / ".build.lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if not force and not _stale():       # another process built it while this one waited
+                return LIB_PATH
+            return _build_locked(verbose)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+
+
+def _build_locked(verbose: bool) -> Path:
     nvcc = _nvcc()
     objs = []
     for src in SOURCES:
@@ -58,8 +72,10 @@ def build(force: bool = False, verbose: bool = False) -> Path:
             print(" ".join(cmd), file=sys.stderr)
         subprocess.run(cmd, check=True)
         objs.append(str(obj))
-    cmd = [nvcc, "-shared", "-o", str(LIB_PATH), *objs, "-gencode", "arch=compute_100a,code=sm_100a"]
+    tmp = LIB_PATH.with_suffix(".so.tmp")       # linked beside the target, then moved into place in one step
+    cmd = [nvcc, "-shared", "-o", str(tmp), *objs, "-gencode", "arch=compute_100a,code=sm_100a"]
     subprocess.run(cmd, check=True)
+    os.replace(tmp, LIB_PATH)
     return LIB_PATH
 
 

@@ -15,8 +15,11 @@
 //                       memory, K-major, 128-byte swizzle) and O_t += P_t V_j
 //                       (A = P_t from tensor memory, B = V_j MN-major). S_0, S_1,
 //                       O_0, O_1 are 128-column fp32 accumulators in TMEM.
-//   warps 10-11         idle; they only give their registers to the softmax groups
-//                       (setmaxnreg: 208 registers per softmax thread, 88 elsewhere).
+//   warps 10-11         give their registers to the softmax groups (setmaxnreg: 208 registers
+//                       per softmax thread, 88 elsewhere). In head-exchange use they do the
+//                       exchange: QK-norm + RoPE of this rank's raw Q, K and peer stores of every
+//                       head row to the rank that attends it, while the other roles already work
+//                       on what has arrived (ExchangeParams). Idle otherwise.
 //
 // Issue order per key/value tile j:  S0_j, PV1_{j-1}, S1_j, PV0_j.  While one
 // softmax group works on its S, the tensor pipe runs the other tile's two MMAs.
@@ -36,6 +39,7 @@
 
 #include "attn_launch.h"
 #include "ptx.cuh"
+#include "row_math.cuh"
 #include "softmax_row.cuh"
 
 #include <cuda_bf16.h>
@@ -138,6 +142,71 @@ __device__ __forceinline__ void issue_pv_part(uint32_t d_tmem, uint32_t p_tmem, 
     }
 }
 
+// Head exchange by one of the CTA's two spare warps (see ExchangeParams). Chunk c of the queue:
+// destination order c / (2 n_sub) (0 = this rank itself, then rank - 1, rank - 2, ...: the order in
+// which the destinations get to this rank's segment), then token block, then Q before K+V.
+__device__ __forceinline__ void exchange_rows(const __nv_bfloat16* xin, unsigned char* base, const void* gamma,
+                                              const ExchangeParams& x, int dst_rank, int tok0, int tok1, bool rotate,
+                                              int lane) {
+    const int hl = lane & 15, hw = lane >> 4;
+    const int hpr = x.heads_per_rank;
+    float g[8];
+    if (rotate) unpack8(__ldg(reinterpret_cast<const uint4*>(gamma) + hl), g);
+    // A half-warp takes a token per iteration, four head rows at a time (four 16-byte loads in
+    // flight per lane).
+    for (int tok = tok0 + hw; tok < tok1; tok += 2) {
+        const uint4* src = reinterpret_cast<const uint4*>(xin + ((long long)tok * x.n_heads_total + dst_rank * hpr) * kHeadDim);
+        uint4* dst = reinterpret_cast<uint4*>(base + ((long long)x.rank * x.s_loc + tok) * hpr * (long long)(kHeadDim * 2));
+        float cs[4], sn[4];
+        if (rotate) {
+            const float4 c4 = __ldg(reinterpret_cast<const float4*>(x.cos_tab + (long long)tok * 64) + hl);
+            const float4 s4 = __ldg(reinterpret_cast<const float4*>(x.sin_tab + (long long)tok * 64) + hl);
+            cs[0] = c4.x; cs[1] = c4.y; cs[2] = c4.z; cs[3] = c4.w;
+            sn[0] = s4.x; sn[1] = s4.y; sn[2] = s4.z; sn[3] = s4.w;
+        }
+        for (int h0 = 0; h0 < hpr; h0 += 4) {
+            uint4 raw[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (h0 + u < hpr) raw[u] = __ldg(src + (h0 + u) * 16 + hl);
+#pragma unroll
+            for (int u = 0; u < 4; ++u)      // (the shuffles of norm_rope_row stay inside a half-warp)
+                if (h0 + u < hpr) dst[(h0 + u) * 16 + hl] = rotate ? norm_rope_row(raw[u], g, cs, sn, x.eps) : raw[u];
+        }
+    }
+}
+
+__device__ __forceinline__ void exchange_role(const ExchangeParams& x, int lane) {
+    const int n_sub = (x.s_loc + kExchangeTokens - 1) / kExchangeTokens;
+    const int n_tiles = (x.s_loc + kTileM - 1) / kTileM;
+    const unsigned int per_dest = 2u * n_sub, total = per_dest * x.world;
+    for (;;) {
+        unsigned int c = 0;
+        if (lane == 0) c = atomicAdd(x.next_chunk, 1u);
+        c = __shfl_sync(0xffffffffu, c, 0);
+        if (c >= total) break;
+        const int dst_rank = (x.rank - (int)(c / per_dest) + x.world) % x.world;
+        const unsigned int r = c % per_dest;
+        const int kind = (int)(r & 1u);                       // 0: Q rows, 1: K and V rows
+        const int tok0 = (int)(r >> 1) * kExchangeTokens;
+        const int tok1 = min(tok0 + kExchangeTokens, x.s_loc);
+        // one inlined copy of the row loop: Q; or K, then V (a runtime loop over the tensors)
+#pragma unroll 1
+        for (int pass = 0; pass <= kind; ++pass) {
+            const bool is_v = kind == 1 && pass == 1;
+            const void* xin = kind == 0 ? x.q : (is_v ? x.v : x.k);
+            unsigned char* base = kind == 0 ? x.dst_q[dst_rank] : (is_v ? x.dst_v[dst_rank] : x.dst_k[dst_rank]);
+            exchange_rows(static_cast<const __nv_bfloat16*>(xin), base, kind == 0 ? x.gamma_q : x.gamma_k, x, dst_rank, tok0,
+                          tok1, !is_v, lane);
+        }
+        __syncwarp();
+        if (lane == 0) {
+            __threadfence_system();            // this warp's stores, wherever they went, before the count
+            atomicAdd_system(x.tile_words[dst_rank] + kind * n_tiles + tok0 / kTileM, 1u);
+        }
+    }
+}
+
 }  // namespace
 
 __global__ void __launch_bounds__(kThreads, 1)
@@ -150,8 +219,8 @@ attn_fwd_sm100_kernel(const __grid_constant__ AttnParams p) {
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int pair = blockIdx.x;
-    const int head = blockIdx.y;
+    const int pair = p.grid_head_fastest ? blockIdx.y : blockIdx.x;
+    const int head = p.grid_head_fastest ? blockIdx.x : blockIdx.y;
     const int bidx = blockIdx.z;
     const int n_kv = p.n_kv_tiles;
     // With an odd number of query tiles the last CTA of a (batch, head) has one tile only: its
@@ -201,7 +270,11 @@ attn_fwd_sm100_kernel(const __grid_constant__ AttnParams p) {
                     int seg, row0, valid;
                     locate_tile<kMaxQSeg>(p.q_tile_start, p.q_len, p.n_qseg, qt, seg, row0, valid);
                     if (p.q_ready[seg] != nullptr) {   // the segment is written by another GPU's kernel
-                        ok = global_flag_wait(p.q_ready[seg], p.kv_ready_value, abort_flag, peer_limit);
+                        ok = p.ready_per_tile
+                                 ? global_flag_wait(p.q_ready[seg] + row0 / kTileM,
+                                                    p.ready_uses * (unsigned)((valid + kExchangeTokens - 1) / kExchangeTokens),
+                                                    abort_flag, peer_limit)
+                                 : global_flag_wait(p.q_ready[seg], p.kv_ready_value, abort_flag, peer_limit);
                         if (!ok) break;
                         asm volatile("fence.proxy.async.global;" ::: "memory");
                     }
@@ -215,7 +288,14 @@ attn_fwd_sm100_kernel(const __grid_constant__ AttnParams p) {
                 for (int j = 0; j < n_kv && ok; ++j) {
                     int seg, row0, valid;
                     locate_tile<kMaxKvSeg>(p.kv_tile_start, p.kv_len, p.n_kvseg, j, seg, row0, valid);
-                    if (row0 == 0 && p.kv_ready[seg] != nullptr) {
+                    if (p.ready_per_tile && p.kv_ready[seg] != nullptr) {
+                        // fused head exchange: every tile has its own counter of delivered chunks
+                        ok = global_flag_wait(p.kv_ready[seg] + row0 / kTileN,
+                                              p.ready_uses * (unsigned)((valid + kExchangeTokens - 1) / kExchangeTokens),
+                                              abort_flag, peer_limit);
+                        if (!ok) break;
+                        asm volatile("fence.proxy.async.global;" ::: "memory");
+                    } else if (row0 == 0 && p.kv_ready[seg] != nullptr) {
                         // first tile of a segment that is being copied in: wait for its arrival word,
                         // then order the copy engine's writes before this thread's TMA reads
                         ok = global_flag_wait(p.kv_ready[seg] + head / max(1, p.kv_ready_heads_per_group),
@@ -247,6 +327,9 @@ attn_fwd_sm100_kernel(const __grid_constant__ AttnParams p) {
                         mbar_wait(smem_u32(&ctl->kv_full[i % kStages]), (i / kStages) & 1, &never, lim);
                 }
             }
+        } else if (warp > kMmaWarp) {
+            // ------------------------------ head exchange -----------------------------
+            if (p.xchg.enabled) exchange_role(p.xchg, lane);
         } else if (warp == kMmaWarp) {
             // ------------------------------ MMA issuer --------------------------------
             // The whole warp runs this loop converged; umma_* elect one lane per instruction.
@@ -615,6 +698,7 @@ cudaError_t attn_fwd_launch(const AttnParams& params, cudaStream_t stream) {
     if (peer_words) p.wait_limit_clk += p.peer_wait_limit_clk;
     const size_t smem = attn_fwd_smem_bytes();
     dim3 grid((p.n_q_tiles + 1) / 2, p.n_heads, p.batch);
+    if (p.grid_head_fastest) grid = dim3(p.n_heads, (p.n_q_tiles + 1) / 2, p.batch);
     attn_fwd_sm100_kernel<<<grid, kThreads, smem, stream>>>(p);
     return cudaPeekAtLastError();
 }

@@ -38,6 +38,29 @@ constexpr size_t kStatusBytes = 256;   // every status allocation: the word, pad
 constexpr long long kDefaultWaitClk     = 2000000000ll;    // ~1 s
 constexpr long long kDefaultPeerWaitClk = 40000000000ll;   // ~20 s
 
+// Head exchange done by the attention kernel itself. Rank r holds the raw Q, K, V of its s_loc
+// tokens for all heads; the kernel's two spare warps per CTA normalise + rotate Q and K and store
+// every head row into the memory of the rank that attends that head (peer stores over NVLink; V is
+// copied), while the CTA's other roles already attend to what has arrived. Work is cut into small
+// chunks (kExchangeTokens tokens of one destination rank: their Q rows, or their K and V rows)
+// handed out through a counter, in the order in which the destinations consume them. A finished
+// chunk adds one to the destination's counter of the 128-token tile it belongs to; the consumer's
+// TMA producer waits until a tile's counter has reached (number of steps so far) x (chunks of the
+// tile). Only CTAs that are running take chunks, so no CTA ever waits for work held by a CTA that
+// has not started.
+struct ExchangeParams {
+    const void*  q; const void* k; const void* v;   // [s_loc, n_heads_total, 128] bf16, dense
+    const void*  gamma_q; const void* gamma_k;      // [128] bf16
+    const float* cos_tab; const float* sin_tab;     // [s_loc, 64] fp32: this rank's rows
+    unsigned char* dst_q[8]; unsigned char* dst_k[8]; unsigned char* dst_v[8];   // per destination rank
+    unsigned int*  tile_words[8];                   // destination's counters for this source: [Q | KV][tiles]
+    unsigned int*  next_chunk;                      // local, zero before the launch
+    int   s_loc, n_heads_total, heads_per_rank, world, rank;
+    int   enabled;
+    float eps;
+};
+constexpr int kExchangeTokens = 16;   // tokens per chunk: 8 chunks per 128-token tile
+
 struct AttnParams {
     // 4-D tensor maps, dims (fastest first): head_dim, head, token, batch;
     // box = 64 x 1 x 128 x 1 elements, 128-byte swizzle, zero fill out of bounds.
@@ -78,6 +101,12 @@ struct AttnParams {
     unsigned int        kv_ready_value;
     int                 kv_ready_heads_per_group;
 
+    // Per-tile readiness (fused head exchange): when ready_per_tile is set, q_ready[i] / kv_ready[i]
+    // point at one counter per 128-token tile of segment i; a tile may be fetched once its counter
+    // has reached ready_uses * ceil(tokens in the tile / kExchangeTokens) ("not before", modulo 2^32).
+    int          ready_per_tile;
+    unsigned int ready_uses;
+
     // Head-exchange use (tokens sharded outside the attention, heads inside): query segment i is
     // written into this GPU's memory by rank i's kernel, which then stores kv_ready_value (or a
     // later call's value) to q_ready[i]; the TMA producer waits for that word, bounded, before it
@@ -96,6 +125,13 @@ struct AttnParams {
     unsigned int* fail_flag[8];
     int           n_done;
     unsigned int  done_value;
+
+    // 0: CTAs are numbered pair-fastest (all tile pairs of a head are neighbours: the K/V of a
+    // head are shared through L2 by CTAs that run together). 1: head-fastest, so that the first
+    // CTAs to run are those of the first query segments (head exchange: the local tokens).
+    int grid_head_fastest;
+
+    ExchangeParams xchg;
 };
 
 }  // namespace f2k

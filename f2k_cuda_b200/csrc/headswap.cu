@@ -23,7 +23,19 @@
 //
 // One allocation per rank, exported to the peers by CUDA IPC:
 //     [2 sets] { Qh, Kh, Vh : [world * s_loc, heads/world, 128] ; O : [s_loc, heads, 128] }
-//     control words: arrived[2][world], done[2][world], two counters, failed[2][world].
+//     control words: arrived[2][world], done[2][world], two counters, failed[2][world];
+//     fused form: the chunk queue's counter and delivered-chunk counters [2][world][Q | KV][tiles].
+//
+// Fused form (f2k_hx_forward): steps 1 and 2 are ONE kernel. The attention kernel's two spare warps
+// per CTA do the exchange (same arithmetic, same peer stores), in chunks of 16 tokens taken from a
+// queue in the order the consumers need them, while the other roles of every CTA already attend to
+// the tiles that have arrived (a counter per 128-token tile says how much of it has been
+// delivered): segments are walked in ring order starting with the rank's own tokens, and CTAs are
+// numbered so that those of the local query tokens run first. The exchange (NVLink time of 3
+// shards) then hides under the attention instead of preceding it. On ONE GPU several ranks cannot
+// run this form side by side (a rank's kernel fills the GPU and would wait for a kernel that
+// cannot start), so the in-process emulation of the tests uses the two-kernel form; the fused form
+// is tested with world 1 on one GPU and with one process per GPU.
 
 #include "f2k_attn.h"
 
@@ -87,6 +99,17 @@ struct f2k_hx {
     // failed[set][src]: rank src stores the step number here when a CTA of its attention kernel gave
     // up, before it publishes done[set][src]: its heads of this rank's rows were not all written
     unsigned int* failed(unsigned char* base, int set, int src) const { return words(base) + 40 + set * 8 + src; }
+    // fused form (f2k_hx_forward): the chunk queue's counter, and behind the control header one
+    // counter of delivered chunks per (buffer set, source rank, Q | K+V, 128-token tile)
+    unsigned int* next_chunk() const { return words(buf) + 96; }
+    static constexpr size_t kControlBytes = 1024;
+    int n_tiles = 0;
+    unsigned int set_uses[2] = {0, 0};       // fused steps run on each buffer set so far
+    unsigned int* tile_words(unsigned char* base, int set, int src) const {   // [Q tiles | KV tiles]
+        return reinterpret_cast<unsigned int*>(base + flags_off + kControlBytes) + ((size_t)set * cfg.world + src) * 2 * n_tiles;
+    }
+    AttnParams fparams[2];                   // fused form, per buffer set
+    bool       have_fparams[2] = {false, false};
 };
 
 namespace {
@@ -131,7 +154,9 @@ int f2k_hx_create(const f2k_seqpar_config* cfg, f2k_hx** out) {
     h->scale = cfg->scale > 0.f ? cfg->scale : 1.0f / std::sqrt((float)cfg->head_dim);
     h->shard_bytes = (size_t)cfg->seq_local * cfg->n_heads * kHeadDim * 2;     // = world*s_loc*hpr*256
     h->flags_off   = 8 * h->shard_bytes;
-    h->total_bytes = h->flags_off + 256;
+    h->n_tiles     = (cfg->seq_local + kTileM - 1) / kTileM;
+    h->total_bytes = h->flags_off + f2k_hx::kControlBytes +
+                     ((size_t)2 * cfg->world * 2 * h->n_tiles * sizeof(unsigned int) + 255) / 256 * 256;
 
     int dev = 0, major = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -148,7 +173,7 @@ int f2k_hx_create(const f2k_seqpar_config* cfg, f2k_hx** out) {
     if (e != cudaSuccess) return fail_cuda(h, "kernel load", e);
     e = cudaMalloc(reinterpret_cast<void**>(&h->buf), h->total_bytes);
     if (e != cudaSuccess) return fail_cuda(h, "cudaMalloc(exchange buffer)", e);
-    e = cudaMemset(h->buf + h->flags_off, 0, 256);
+    e = cudaMemset(h->buf + h->flags_off, 0, h->total_bytes - h->flags_off);
     if (e != cudaSuccess) return fail_cuda(h, "cudaMemset(flags)", e);
     e = cudaMalloc(reinterpret_cast<void**>(&h->d_status), kStatusBytes);
     if (e == cudaSuccess) e = cudaMemset(h->d_status, 0, kStatusBytes);
@@ -186,6 +211,7 @@ int f2k_hx_attach(f2k_hx* h, void* const* peer_bases) {
         h->peer[r] = static_cast<unsigned char*>(peer_bases[r]);
     }
     h->have_params[0] = h->have_params[1] = false;
+    h->have_fparams[0] = h->have_fparams[1] = false;
     return F2K_OK;
 }
 
@@ -274,6 +300,87 @@ int f2k_hx_attend(f2k_hx* h, void* stream) {
     p.wait_limit_clk      = h->wait_clk;
     p.peer_wait_limit_clk = h->peer_wait_clk;
     const cudaError_t e = attn_fwd_launch(p, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail_cuda(h, "attention launch", e);
+    h->phase = f2k_hx::kAttended;
+    return F2K_OK;
+}
+
+int f2k_hx_forward(f2k_hx* h, const void* q_raw, const void* k_raw, const void* v, const void* gamma_q,
+                   const void* gamma_k, const float* cos_local, const float* sin_local, float eps, void* stream) {
+    if (!h || !h->valid) return F2K_ERR_INVALID;
+    if (!q_raw || !k_raw || !v || !gamma_q || !gamma_k || !cos_local || !sin_local)
+        return fail(h, F2K_ERR_INVALID, "null tensor pointer");
+    for (const void* ptr : {q_raw, k_raw, v, gamma_q, gamma_k, static_cast<const void*>(cos_local),
+                            static_cast<const void*>(sin_local)})
+        if ((reinterpret_cast<uintptr_t>(ptr) & 15u) != 0)
+            return fail(h, F2K_ERR_INVALID, "tensor, gain and table pointers must be 16-byte aligned");
+    const f2k_seqpar_config& c = h->cfg;
+    for (int r = 0; r < c.world; ++r)
+        if (!h->peer[r]) return fail(h, F2K_ERR_INVALID, "peers not attached");
+    if (h->phase != f2k_hx::kIdle)
+        return fail(h, F2K_ERR_INVALID, "forward before the previous step's output");
+    h->epoch += 1;
+    const int set = h->epoch & 1;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    AttnParams& p = h->fparams[set];
+    if (!h->have_fparams[set]) {
+        std::memset(&p, 0, sizeof p);
+        const long long tok_h = (long long)h->hpr * kHeadDim;          // token stride of the head-sharded tensors
+        const long long tok_o = (long long)c.n_heads * kHeadDim;       // token stride of the token-sharded output
+        const int tiles_per_seg = (c.seq_local + kTileM - 1) / kTileM;
+        const size_t seg_bytes = (size_t)c.seq_local * h->hpr * kHeadDim * 2;
+        for (int i = 0; i < c.world; ++i) {                            // segment i = the tokens of rank (rank + i) % world
+            const int src = (c.rank + i) % c.world;
+            if (!encode(h, &p.tm_q[i], h->part(h->buf, set, 0) + src * seg_bytes, c.seq_local, h->hpr, tok_h) ||
+                !encode(h, &p.tm_k[i], h->part(h->buf, set, 1) + src * seg_bytes, c.seq_local, h->hpr, tok_h) ||
+                !encode(h, &p.tm_v[i], h->part(h->buf, set, 2) + src * seg_bytes, c.seq_local, h->hpr, tok_h))
+                return fail(h, F2K_ERR_CUDA, "tensor map failed");
+            p.o_ptr[i] = h->part(h->peer[src], set, 3) + (size_t)c.rank * h->hpr * kHeadDim * 2;
+            p.o_tok_stride[i]   = tok_o;
+            p.o_batch_stride[i] = tok_o * c.seq_local;
+            p.q_len[i] = p.kv_len[i] = c.seq_local;
+            p.q_tile_start[i] = p.kv_tile_start[i] = i * tiles_per_seg;
+            p.q_ready[i]  = h->tile_words(h->buf, set, src);            // own rows too: the exchange is part of this kernel
+            p.kv_ready[i] = h->tile_words(h->buf, set, src) + h->n_tiles;
+            p.done_flag[i] = h->done(h->peer[src], set, c.rank);
+            p.fail_flag[i] = h->failed(h->peer[src], set, c.rank);
+        }
+        p.q_tile_start[c.world] = p.kv_tile_start[c.world] = c.world * tiles_per_seg;
+        p.n_qseg = p.n_kvseg = c.world;
+        p.n_q_tiles = p.n_kv_tiles = c.world * tiles_per_seg;
+        p.kv_ready_heads_per_group = h->hpr;
+        p.n_heads = h->hpr;
+        p.batch = 1;
+        p.scale_log2 = h->scale * 1.4426950408889634f;
+        p.status = h->d_status;
+        p.done_counter = h->counter(1);
+        p.n_done = c.world;
+        p.grid_head_fastest = 1;
+        p.ready_per_tile = 1;
+        ExchangeParams& x = p.xchg;
+        for (int d = 0; d < c.world; ++d) {
+            x.dst_q[d] = h->part(h->peer[d], set, 0);
+            x.dst_k[d] = h->part(h->peer[d], set, 1);
+            x.dst_v[d] = h->part(h->peer[d], set, 2);
+            x.tile_words[d] = h->tile_words(h->peer[d], set, c.rank);
+        }
+        x.next_chunk = h->next_chunk();
+        x.s_loc = c.seq_local; x.n_heads_total = c.n_heads; x.heads_per_rank = h->hpr; x.world = c.world; x.rank = c.rank;
+        x.enabled = 1;
+        h->have_fparams[set] = true;
+    }
+    p.kv_ready_value = h->epoch;
+    p.done_value = h->epoch;
+    p.wait_limit_clk      = h->wait_clk;
+    p.peer_wait_limit_clk = h->peer_wait_clk;
+    p.xchg.q = q_raw; p.xchg.k = k_raw; p.xchg.v = v;
+    p.xchg.gamma_q = gamma_q; p.xchg.gamma_k = gamma_k;
+    p.xchg.cos_tab = cos_local; p.xchg.sin_tab = sin_local;
+    p.xchg.eps = eps;
+    p.ready_uses = ++h->set_uses[set];
+    cudaError_t e = cudaMemsetAsync(h->next_chunk(), 0, sizeof(unsigned int), s);   // the chunk queue starts at its head
+    if (e != cudaSuccess) return fail_cuda(h, "cudaMemsetAsync(chunk counters)", e);
+    e = attn_fwd_launch(p, s);
     if (e != cudaSuccess) return fail_cuda(h, "attention launch", e);
     h->phase = f2k_hx::kAttended;
     return F2K_OK;

@@ -107,6 +107,13 @@ class HeadExchangeAttention:
         return lib.f2k_hx_exchange_in(self._h, p(q_raw), p(k_raw), p(v), p(gamma_q), p(gamma_k), p(cos_local),
                                       p(sin_local), eps, self._stream(stream)) == _lib.F2K_OK
 
+    def forward(self, q_raw, k_raw, v, gamma_q, gamma_k, cos_local, sin_local, eps: float, stream=None) -> bool:
+        """exchange_in + attend as one kernel (the exchange runs on the attention kernel's spare
+        warps and hides under the attention). One process per GPU, or world == 1."""
+        p = lambda t: C.c_void_p(t.data_ptr())  # noqa: E731
+        return lib.f2k_hx_forward(self._h, p(q_raw), p(k_raw), p(v), p(gamma_q), p(gamma_k), p(cos_local),
+                                  p(sin_local), eps, self._stream(stream)) == _lib.F2K_OK
+
     def attend(self, stream=None) -> bool:
         return lib.f2k_hx_attend(self._h, self._stream(stream)) == _lib.F2K_OK
 

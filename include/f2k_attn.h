@@ -310,6 +310,15 @@ int f2k_hx_exchange_in(f2k_hx* h, const void* q_raw, const void* k_raw, const vo
                        const void* gamma_q, const void* gamma_k,
                        const float* cos_local, const float* sin_local, float eps, void* stream);
 int f2k_hx_attend(f2k_hx* h, void* stream);
+/* exchange_in and attend as ONE kernel: the attention kernel's spare warps do the exchange (same
+ * arithmetic, same peer stores) while its other warps already attend to what has arrived, local
+ * tokens first, so that the exchange's NVLink time hides under the attention. Same arguments as
+ * exchange_in; followed by f2k_hx_output like attend. For one process per GPU: several ranks on
+ * ONE GPU cannot run this form side by side (each kernel fills the GPU and would wait for the
+ * others' exchange); world == 1 works anywhere. */
+int f2k_hx_forward(f2k_hx* h, const void* q_raw, const void* k_raw, const void* v,
+                   const void* gamma_q, const void* gamma_k,
+                   const float* cos_local, const float* sin_local, float eps, void* stream);
 /* Makes `stream` wait until every rank has written its heads of this rank's rows; *o_local is
  * then this rank's [seq_local, n_heads, 128] bf16 output (inside the exchange buffer; valid
  * until the exchange_in after next). */

@@ -39,13 +39,18 @@ def main():
                                              gammas=(None, None, p.gammas[2], p.gammas[3]),
                                              tables=(None, None, cos, sin), eps=1e-6)
     dist.barrier()
-    for step in range(4):                        # back to back: no collective, no host synchronisation between steps
-        assert hx.exchange_in(q, k, v, gq, gk, dcos, dsin, 1e-6), hx.last_error()
-        assert hx.attend(), hx.last_error()
+    # back to back: no collective, no host synchronisation between steps. Steps 0-3 run the exchange
+    # as a kernel of its own, steps 4-7 inside the attention kernel (the fused form).
+    for step in range(8):
+        if step < 4:
+            assert hx.exchange_in(q, k, v, gq, gk, dcos, dsin, 1e-6), hx.last_error()
+            assert hx.attend(), hx.last_error()
+        else:
+            assert hx.forward(q, k, v, gq, gk, dcos, dsin, 1e-6), hx.last_error()
         o = hx.output()
         assert o is not None, hx.last_error()
         got = o.clone()                          # stream order: after the waits of output()
-        if step in (0, 3):
+        if step in (0, 3, 4, 7):
             torch.cuda.synchronize()
             assert hx.device_status() == 0, hx.last_error()
             assert_parity(host_f32(got), ref[:, sl], f"rank {rank} step {step}")

@@ -70,6 +70,44 @@ def test_all_ranks_in_one_process(orc, world, per, H):
             assert_parity(host_f32(o), ref[:, r * per:(r + 1) * per], f"world {world} rank {r} step {step}")
 
 
+@pytest.mark.parametrize("per,H", [(300, 2), (1088, 4), (129, 5)])
+@pytest.mark.timeout(120, method="thread")
+def test_exchange_inside_the_attention_kernel_world_1(orc, per, H):
+    """The fused form (f2k_hx_forward): the attention kernel's spare warps normalise, rotate and
+    deliver Q, K, V while its other warps wait for the arrival words and attend. With one rank the
+    whole mechanism (chunk queue, per-destination counters, arrival words for K/V and for Q, head-
+    fastest CTA numbering) runs on one GPU in one kernel. Three steps: both buffer sets, then the
+    first again; heads not a multiple of four take the exchange's narrower path."""
+    import torch
+    from f2k_cuda_b200.headswap import HeadExchangeAttention
+    from f2k_cuda_b200.inputs import Workload, make_problem
+    w = Workload("hxf", 1, 0, ((1, per),), seed=0xF05E + per)
+    p = make_problem(w, heads=H)
+    cos, sin, ref = reference_output(orc, w, p)
+    hx = HeadExchangeAttention(per, H, 128, 1, 0)
+    assert hx.ok(), hx.last_error()
+    assert hx.attach_in_process([hx])
+    gq, gk = dev_bf16(p.gammas[2]), dev_bf16(p.gammas[3])
+    dcos, dsin = torch.from_numpy(cos).cuda(), torch.from_numpy(sin).cuda()
+    q, k, v = dev_bf16(p.q_img), dev_bf16(p.k_img), dev_bf16(p.v_img)
+    keep = [x.clone() for x in (q, k, v)]
+    for step in range(3):
+        assert hx.forward(q, k, v, gq, gk, dcos, dsin, 1e-6), hx.last_error()
+        o = hx.output()
+        assert o is not None, hx.last_error()
+        torch.cuda.synchronize()
+        assert hx.device_status() == 0, hx.last_error()
+        assert_parity(host_f32(o), ref, f"fused exchange step {step}")
+    assert all(torch.equal(a, b) for a, b in zip(keep, (q, k, v)))        # the raw tensors are only read
+    fused_bits = o.clone()
+    # the same arithmetic as the two-kernel form: identical bits
+    assert hx.exchange_in(q, k, v, gq, gk, dcos, dsin, 1e-6) and hx.attend(), hx.last_error()
+    o2 = hx.output()
+    torch.cuda.synchronize()
+    assert hx.device_status() == 0
+    assert torch.equal(o2, fused_bits), "fused and two-kernel forms must agree bit for bit"
+
+
 def test_equals_the_single_gpu_fused_call_bit_for_bit(orc):
     """Same kernels, same arithmetic: the exchanged result must equal the one-GPU fused call."""
     import torch
