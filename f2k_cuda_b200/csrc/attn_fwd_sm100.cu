@@ -67,11 +67,8 @@ constexpr float kLazyThreshold = 8.0f;  // log2 units
 #ifndef F2K_OPT_P_PARTS
 #define F2K_OPT_P_PARTS 4      // P is handed to the MMA warp in this many parts (1, 2 or 4)
 #endif
-#ifndef F2K_OPT_SPEC_MAX
-#define F2K_OPT_SPEC_MAX 0     // start the exponentials of a row before its maximum is known (see the softmax loop)
-#endif
 #ifndef F2K_OPT_POLY_OF8
-#define F2K_OPT_POLY_OF8 0     // of every 8 key pairs, how many take 2^x on the FMA pipe (0..8)
+#define F2K_OPT_POLY_OF8 0     // of every 8 key pairs, how many take 2^x on the FMA pipe (0..8); see softmax_row.cuh
 #endif
 constexpr int kPParts = F2K_OPT_P_PARTS;
 #ifndef F2K_OPT_REGS_SOFTMAX
@@ -436,102 +433,6 @@ attn_fwd_sm100_kernel(const __grid_constant__ AttnParams p) {
             if (!ok) break;
             tc_fence_after_sync();
 
-#if F2K_OPT_SPEC_MAX
-            // The row is fetched in two halves. The exponentials of the first half are started at
-            // once, against the exponent reference the row already has, while the second half is on
-            // its way and the maxima of both halves are folded on the other pipes: after the first
-            // tiles the reference rarely moves (lazy threshold), so the row maximum is off the
-            // critical path. When it does move (always on the first tile), the reference is updated,
-            // O rescaled, and the first half is redone before anything of it is handed over.
-            uint32_t s[128];
-            float mx[kMaxChains];
-            float sum[4];
-            {
-                uint32_t(&s0)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[0]);
-                uint32_t(&s1)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[32]);
-                uint32_t(&s2)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[64]);
-                uint32_t(&s3)[32] = *reinterpret_cast<uint32_t(*)[32]>(&s[96]);
-                tmem_ld_x32(tS + 0, s0);
-                tmem_ld_x32(tS + 32, s1);
-                tmem_wait_ld();
-                tmem_ld_x32(tS + 64, s2);
-                tmem_ld_x32(tS + 96, s3);
-            }
-            if (valid < 64) {  // last tile of a segment: keys past its end do not exist
-#pragma unroll
-                for (int i = 0; i < 64; ++i)
-                    if (i >= valid) s[i] = __float_as_uint(-INFINITY);
-            }
-            float neg_mc = -m_ref * c;
-            sum[0] = sum[1] = sum[2] = sum[3] = 0.f;
-#pragma unroll
-            for (int q = 0; q < 2; ++q) {
-                uint32_t pk[16];
-                exp_chunk16<F2K_OPT_POLY_OF8>(&s[q * 32], pk, c, neg_mc, sum);
-                exp_chunk16<F2K_OPT_POLY_OF8>(&s[q * 32 + 16], pk + 8, c, neg_mc, sum);
-                tmem_st_x16(tS + q * 16, pk);
-            }
-            row_max64<true>(&s[0], mx);
-            tmem_wait_ld();
-            if (valid < kTileN) {
-#pragma unroll
-                for (int i = 64; i < 128; ++i)
-                    if (i >= valid) s[i] = __float_as_uint(-INFINITY);
-            }
-            row_max64<false>(&s[64], mx);
-            const float m_tile = row_max_finish(mx);
-            const bool need = !((m_tile - m_ref) * c <= kLazyThreshold);   // also true for a NaN of inf - inf
-            if (__any_sync(0xffffffffu, need)) {
-                tmem_wait_st();     // the stores of the first attempt land before their slots are written again
-                const float m_new = fmaxf(m_ref, m_tile);
-                const float f = ex2_approx((m_ref - m_new) * c);
-                l_sum *= f;
-                m_ref = m_new;
-                neg_mc = -m_ref * c;
-                if (j > 0) {
-                    // Rescale this row of O in place (O_t is idle, see the file header).
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        uint32_t o[32];
-                        tmem_ld_x32(tO + q * 32, o);
-                        tmem_wait_ld();
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
-                        tmem_st_x32(tO + q * 32, o);
-                    }
-                }
-                sum[0] = sum[1] = sum[2] = sum[3] = 0.f;
-#pragma unroll
-                for (int q = 0; q < 2; ++q) {      // the first half again, against the new reference
-                    uint32_t pk[16];
-                    exp_chunk16<0>(&s[q * 32], pk, c, neg_mc, sum);
-                    exp_chunk16<0>(&s[q * 32 + 16], pk + 8, c, neg_mc, sum);
-                    tmem_st_x16(tS + q * 16, pk);
-                }
-            }
-            // hand the first half over (one or two parts), then the second half chunk by chunk,
-            // each part announced half a chunk after its last store was issued
-            int pending = kPParts >= 2 ? kPParts / 2 - 1 : -1;
-            if (kPParts == 4) {
-                tmem_wait_st();
-                tc_fence_before_sync();
-                mbar_arrive(smem_u32(&ctl->p_full[t][0]));
-            }
-#pragma unroll
-            for (int q = 2; q < 4; ++q) {
-                uint32_t pk[16];
-                exp_chunk16<F2K_OPT_POLY_OF8>(&s[q * 32], pk, c, neg_mc, sum);
-                if (pending >= 0) {
-                    tmem_wait_st();
-                    tc_fence_before_sync();
-                    mbar_arrive(smem_u32(&ctl->p_full[t][0]) + pending * 8);
-                    pending = -1;
-                }
-                exp_chunk16<F2K_OPT_POLY_OF8>(&s[q * 32 + 16], pk + 8, c, neg_mc, sum);
-                tmem_st_x16(tS + q * 16, pk);
-                if ((q + 1) % (4 / kPParts) == 0) pending = (q + 1) / (4 / kPParts) - 1;
-            }
-#else
             // The row is fetched in two halves: the maxima of the first 64 scores are folded while
             // the second 64 are still on their way from tensor memory.
             uint32_t s[128];
@@ -604,7 +505,6 @@ attn_fwd_sm100_kernel(const __grid_constant__ AttnParams p) {
                 tmem_st_x16(tS + q * 16, pk);
                 if ((q + 1) % (4 / kPParts) == 0) pending = (q + 1) / (4 / kPParts) - 1;
             }
-#endif
             tmem_wait_st();
             tc_fence_before_sync();
             mbar_arrive(smem_u32(&ctl->p_full[t][kPParts - 1]));

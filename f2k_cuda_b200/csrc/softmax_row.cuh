@@ -5,10 +5,13 @@
 //   exp_chunk16     P = 2^(c*s + neg_mc) for 16 scores -> 8 packed bf16 pairs, and the sum of
 //                   the unrounded values (four partial sums)
 //
-// 2^x comes from two places so that neither pipe is the bottleneck: the special-function
-// unit (ex2.approx, 4 lanes per clock per scheduler) and a cubic polynomial on the FMA pipe
-// (`kPolyOf8` of every 8 key pairs). Both agree to better than 1e-4 relative, far inside the
-// bf16 rounding P goes through next.
+// 2^x comes from two places: the special-function unit (ex2.approx, 4 lanes per clock per
+// scheduler; the two softmax groups of a CTA share it) and a cubic polynomial on the FMA pipe for
+// `kPolyOf8` of every 8 key pairs. Both agree to better than 1e-4 relative, far inside the bf16
+// rounding P goes through next. Measured on the 4608-token shape, the polynomial share does not
+// pay: 1 of 8 pairs came out between 1.3 % faster and 7 % slower than none depending on how the
+// rest of the kernel happened to be scheduled, 2 of 8 and more always slower (the polynomial
+// costs issue slots the row needs elsewhere). It ships switched off (F2K_OPT_POLY_OF8 = 0).
 #pragma once
 
 #include "ptx.cuh"
@@ -40,27 +43,11 @@ __device__ __forceinline__ float row_max_finish(const float (&m)[kMaxChains]) {
         return fmaxf(fmax3(m[0], m[1], m[2]), m[3]);
 }
 
-// 2^x for a pair on the FMA pipe. x = n + f by the 1.5*2^23 rounding trick, cubic fit of 2^f on
-// [-0.5, 0.5], exponent patched in with an integer shift-add. x is clamped at -126 so that the
-// exponent arithmetic cannot wrap (the result is then ~2^-126, i.e. nothing).
-__device__ __forceinline__ void exp2_fma_pair(float& r0, float& r1, float x0, float x1) {
-    using namespace f2k::ptx;
-    constexpr float kMagic = 12582912.0f;  // 1.5 * 2^23
-    x0 = fmaxf(x0, -126.0f);
-    x1 = fmaxf(x1, -126.0f);
-    float t0, t1, n0, n1, f0, f1, p0, p1;
-    add2(t0, t1, x0, x1, kMagic, kMagic);
-    add2(n0, n1, t0, t1, -kMagic, -kMagic);
-    add2(f0, f1, x0, x1, -n0, -n1);
-    fma2(p0, p1, f0, f1, 0.0550886838f, 0.0550886838f, 0.242604051f, 0.242604051f);
-    fma2(p0, p1, p0, p1, f0, f1, 0.693276242f, 0.693276242f);
-    fma2(p0, p1, p0, p1, f0, f1, 0.99992894f, 0.99992894f);
-    r0 = __uint_as_float((__float_as_uint(t0) << 23) + __float_as_uint(p0));
-    r1 = __uint_as_float((__float_as_uint(t1) << 23) + __float_as_uint(p1));
-}
-
-// The same for one argument with scalar instructions (six FMA-pipe operations, one clamp and one
-// shift-add on the integer pipe).
+// 2^x on the FMA pipe: x = n + f by the 1.5*2^23 rounding trick, cubic fit of 2^f on [-0.5, 0.5]
+// (relative error < 1e-4, far inside bf16 resolution), exponent patched in with an integer
+// shift-add: six FMA-pipe operations, one clamp and one shift-add. x is clamped at -126 so that
+// the exponent arithmetic cannot wrap (the result is then ~2^-126, i.e. nothing). Scalar on
+// purpose: the packed f32x2 form measured slower inside the kernel.
 __device__ __forceinline__ float exp2_fma_scalar(float x) {
     constexpr float kMagic = 12582912.0f;  // 1.5 * 2^23
     x = fmaxf(x, -126.0f);
@@ -71,10 +58,6 @@ __device__ __forceinline__ float exp2_fma_scalar(float x) {
     p = __fmaf_rn(p, f, 0.99992894f);
     return __uint_as_float((__float_as_uint(t) << 23) + __float_as_uint(p));
 }
-#ifndef F2K_OPT_POLY_SCALAR
-#define F2K_OPT_POLY_SCALAR 0
-#endif
-
 // 16 scores -> 8 packed bf16 pairs. `pair0` is the index of the first pair inside its group of 8
 // pairs (0 or 8 key pairs into a 32-key chunk), which decides who takes the polynomial.
 template <int kPolyOf8>
@@ -92,17 +75,10 @@ __device__ __forceinline__ void exp_chunk16(const uint32_t* s, uint32_t* pk, flo
         const bool poly_a = ((pa + 1) * kPolyOf8 / 8) != (pa * kPolyOf8 / 8);
         const bool poly_b = ((pb + 1) * kPolyOf8 / 8) != (pb * kPolyOf8 / 8);
         float p0, p1, p2, p3;
-#if F2K_OPT_POLY_SCALAR
         if (poly_a) { p0 = exp2_fma_scalar(x0); p1 = exp2_fma_scalar(x1); }
         else { p0 = ex2_approx(x0); p1 = ex2_approx(x1); }
         if (poly_b) { p2 = exp2_fma_scalar(x2); p3 = exp2_fma_scalar(x3); }
         else { p2 = ex2_approx(x2); p3 = ex2_approx(x3); }
-#else
-        if (poly_a) exp2_fma_pair(p0, p1, x0, x1);
-        else { p0 = ex2_approx(x0); p1 = ex2_approx(x1); }
-        if (poly_b) exp2_fma_pair(p2, p3, x2, x3);
-        else { p2 = ex2_approx(x2); p3 = ex2_approx(x3); }
-#endif
         add2(sum[0], sum[1], sum[0], sum[1], p0, p1);
         add2(sum[2], sum[3], sum[2], sum[3], p2, p3);
         pk[i / 2 + 0] = pack_bf16x2(p0, p1);
