@@ -87,14 +87,17 @@ struct SmemCtl {
     uint64_t p_full[2][kPParts];   // [tile][part of the key tile]
     uint64_t o_full[2];
     uint64_t drain;
+    uint64_t xchg_full[2][2];      // head exchange: [warp][staging buffer] loaded
     uint32_t tmem_base;
     uint32_t abort;
+    uint32_t softmax_done;         // softmax warps that have finished (head exchange: the spare warps then stop)
 };
 
 constexpr uint32_t kSmemQ    = 0;
 constexpr uint32_t kSmemRing = 2 * kTileBytes;
 constexpr uint32_t kSmemCtl  = kSmemRing + kStages * kTileBytes;
-constexpr uint32_t kSmemUsed = kSmemCtl + sizeof(SmemCtl);
+constexpr uint32_t kSmemStage = (kSmemCtl + sizeof(SmemCtl) + 127u) & ~127u;   // head exchange staging (bulk copies)
+constexpr uint32_t kSmemUsed = kSmemStage + 2 * 2 * (16 * 256 + 4 * 512);
 
 template <int kMax>
 __device__ __forceinline__ void locate_tile(const int* tile_start, const int* len, int nseg,
@@ -142,44 +145,37 @@ __device__ __forceinline__ void issue_pv_part(uint32_t d_tmem, uint32_t p_tmem, 
 // Head exchange by one of the CTA's two spare warps (see ExchangeParams). Chunk c of the queue:
 // destination order c / (2 n_sub) (0 = this rank itself, then rank - 1, rank - 2, ...: the order in
 // which the destinations get to this rank's segment), then token block, then Q before K+V.
-__device__ __forceinline__ void exchange_rows(const __nv_bfloat16* xin, unsigned char* base, const void* gamma,
-                                              const ExchangeParams& x, int dst_rank, int tok0, int tok1, bool rotate,
-                                              int lane) {
-    const int hl = lane & 15, hw = lane >> 4;
-    const int hpr = x.heads_per_rank;
-    float g[8];
-    if (rotate) unpack8(__ldg(reinterpret_cast<const uint4*>(gamma) + hl), g);
-    // A half-warp takes a token per iteration, four head rows at a time (four 16-byte loads in
-    // flight per lane).
-    for (int tok = tok0 + hw; tok < tok1; tok += 2) {
-        const uint4* src = reinterpret_cast<const uint4*>(xin + ((long long)tok * x.n_heads_total + dst_rank * hpr) * kHeadDim);
-        uint4* dst = reinterpret_cast<uint4*>(base + ((long long)x.rank * x.s_loc + tok) * hpr * (long long)(kHeadDim * 2));
-        float cs[4], sn[4];
-        if (rotate) {
-            const float4 c4 = __ldg(reinterpret_cast<const float4*>(x.cos_tab + (long long)tok * 64) + hl);
-            const float4 s4 = __ldg(reinterpret_cast<const float4*>(x.sin_tab + (long long)tok * 64) + hl);
-            cs[0] = c4.x; cs[1] = c4.y; cs[2] = c4.z; cs[3] = c4.w;
-            sn[0] = s4.x; sn[1] = s4.y; sn[2] = s4.z; sn[3] = s4.w;
-        }
-        for (int h0 = 0; h0 < hpr; h0 += 4) {
-            uint4 raw[4];
-#pragma unroll
-            for (int u = 0; u < 4; ++u)
-                if (h0 + u < hpr) raw[u] = __ldg(src + (h0 + u) * 16 + hl);
-#pragma unroll
-            for (int u = 0; u < 4; ++u)      // (the shuffles of norm_rope_row stay inside a half-warp)
-                if (h0 + u < hpr) dst[(h0 + u) * 16 + hl] = rotate ? norm_rope_row(raw[u], g, cs, sn, x.eps) : raw[u];
-        }
-    }
-}
+//
+// Two warps per CTA cannot keep enough loads in flight from registers (measured: 86 GB/s per
+// GPU), so the rows travel as bulk copies through a small staging area in shared memory: one lane
+// issues cp.async.bulk loads of up to 4 KiB of head rows (plus the tokens' cos/sin rows) into one
+// of the warp's two buffers, the warp normalises + rotates the rows in place (a half-warp per
+// row, as the prologue kernel does), and one bulk store sends them to the destination, local or
+// peer. The loads of the next buffer are in flight while this one is worked on.
+constexpr uint32_t kStageRowBytes = 16 * 256;                 // 16 head rows
+constexpr uint32_t kStageTabBytes = 4 * 512;                  // cos + sin rows of up to 4 tokens
+constexpr uint32_t kStageBufBytes = kStageRowBytes + kStageTabBytes;
+constexpr uint32_t kStageBytes    = 2 * 2 * kStageBufBytes;   // 2 warps x 2 buffers
 
-__device__ __forceinline__ void exchange_role(const ExchangeParams& x, int lane) {
+// The warp stops taking chunks once its CTA's softmax groups are done (`softmax_done` reaches 8) if
+// a later CTA will take the CTA's place (`may_stop`: CTAs start in index order, one per SM): that
+// one brings exchange warps of its own. The CTAs of the last wave serve the queue until it is
+// empty, so everything this rank owes its peers is sent. A CTA that waits for rows is running, so
+// its own spare warps keep serving the queue: nothing can stall.
+__device__ __forceinline__ bool exchange_role(const ExchangeParams& x, int lane, uint32_t stage_u32, uint8_t* stage_ptr,
+                                              uint32_t bar0, volatile uint32_t* abort_flag, long long wait_limit,
+                                              volatile uint32_t* softmax_done, bool may_stop) {
+    const int hl = lane & 15, hw = lane >> 4;
     const int n_sub = (x.s_loc + kExchangeTokens - 1) / kExchangeTokens;
     const int n_tiles = (x.s_loc + kTileM - 1) / kTileM;
     const unsigned int per_dest = 2u * n_sub, total = per_dest * x.world;
+    const int hpr = x.heads_per_rank, R = x.unit_rows, tpb = x.tokens_per_buf;
+    const int n_hg = hpr / R;
+    unsigned int fills = 0;                                    // buffers filled so far by this warp: buffer and parity
+    bool ok = true;
     for (;;) {
-        unsigned int c = 0;
-        if (lane == 0) c = atomicAdd(x.next_chunk, 1u);
+        unsigned int c = 0xffffffffu;
+        if (lane == 0 && !(may_stop && *softmax_done >= 8u)) c = atomicAdd(x.next_chunk, 1u);
         c = __shfl_sync(0xffffffffu, c, 0);
         if (c >= total) break;
         const int dst_rank = (x.rank - (int)(c / per_dest) + x.world) % x.world;
@@ -187,21 +183,83 @@ __device__ __forceinline__ void exchange_role(const ExchangeParams& x, int lane)
         const int kind = (int)(r & 1u);                       // 0: Q rows, 1: K and V rows
         const int tok0 = (int)(r >> 1) * kExchangeTokens;
         const int tok1 = min(tok0 + kExchangeTokens, x.s_loc);
-        // one inlined copy of the row loop: Q; or K, then V (a runtime loop over the tensors)
-#pragma unroll 1
-        for (int pass = 0; pass <= kind; ++pass) {
-            const bool is_v = kind == 1 && pass == 1;
-            const void* xin = kind == 0 ? x.q : (is_v ? x.v : x.k);
-            unsigned char* base = kind == 0 ? x.dst_q[dst_rank] : (is_v ? x.dst_v[dst_rank] : x.dst_k[dst_rank]);
-            exchange_rows(static_cast<const __nv_bfloat16*>(xin), base, kind == 0 ? x.gamma_q : x.gamma_k, x, dst_rank, tok0,
-                          tok1, !is_v, lane);
+        const int n_tb = (tok1 - tok0 + tpb - 1) / tpb;
+        const int per_pass = n_hg * n_tb, n_fill = (kind + 1) * per_pass;
+
+        // fill f of the chunk: tensor, head group, token block
+        auto issue = [&](int f) {                              // lane 0 only
+            const int pass = f / per_pass, rem = f % per_pass, hg = rem / n_tb, t0 = tok0 + (rem % n_tb) * tpb;
+            const int nt = min(tpb, tok1 - t0);
+            const bool rot = !(kind == 1 && pass == 1);
+            const __nv_bfloat16* xin = static_cast<const __nv_bfloat16*>(kind == 0 ? x.q : (pass == 0 ? x.k : x.v));
+            const unsigned int n = fills;
+            const uint32_t buf = stage_u32 + (n & 1u) * kStageBufBytes, bar = bar0 + (n & 1u) * 8;
+            bulk_wait_read<0>();                               // the store that last used this buffer has read it
+            mbar_arrive_expect_tx(bar, (uint32_t)nt * (uint32_t)(R * 256 + (rot ? 512 : 0)));
+            for (int i = 0; i < nt; ++i) {
+                bulk_load(buf + i * R * 256, xin + ((long long)(t0 + i) * x.n_heads_total + dst_rank * hpr + hg * R) * kHeadDim,
+                          R * 256, bar);
+                if (rot) {
+                    bulk_load(buf + kStageRowBytes + i * 512, x.cos_tab + (long long)(t0 + i) * 64, 256, bar);
+                    bulk_load(buf + kStageRowBytes + i * 512 + 256, x.sin_tab + (long long)(t0 + i) * 64, 256, bar);
+                }
+            }
+        };
+        if (lane == 0) issue(0);
+        for (int f = 0; f < n_fill; ++f) {
+            const unsigned int n = fills;                      // the buffer fill f went into
+            ++fills;
+            if (f + 1 < n_fill && lane == 0) issue(f + 1);
+            __syncwarp();
+            ok = mbar_wait(bar0 + (n & 1u) * 8, (n >> 1) & 1u, abort_flag, wait_limit);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            const int pass = f / per_pass, rem = f % per_pass, hg = rem / n_tb, t0 = tok0 + (rem % n_tb) * tpb;
+            const int nt = min(tpb, tok1 - t0);
+            const bool rot = !(kind == 1 && pass == 1);
+            uint8_t* buf = stage_ptr + (n & 1u) * kStageBufBytes;
+            if (rot) {
+                float g[8];
+                unpack8(__ldg(reinterpret_cast<const uint4*>(kind == 0 ? x.gamma_q : x.gamma_k) + hl), g);
+                for (int row = hw; row < nt * R; row += 2) {   // a half-warp per row; both halves run the same count
+                    const int ti = row / R;
+                    uint4* cell = reinterpret_cast<uint4*>(buf + row * 256) + hl;
+                    const float4 c4 = *(reinterpret_cast<const float4*>(buf + kStageRowBytes + ti * 512) + hl);
+                    const float4 s4 = *(reinterpret_cast<const float4*>(buf + kStageRowBytes + ti * 512 + 256) + hl);
+                    const float cs[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
+                    *cell = norm_rope_row(*cell, g, cs, sn, x.eps);
+                }
+                fence_proxy_async_smem();                      // the rewritten rows, before the bulk store reads them
+            }
+            __syncwarp();
+            if (lane == 0) {
+                unsigned char* base = kind == 0 ? x.dst_q[dst_rank] : (pass == 0 ? x.dst_k[dst_rank] : x.dst_v[dst_rank]);
+                unsigned char* dst = base + (((long long)x.rank * x.s_loc + t0) * hpr + hg * R) * (long long)(kHeadDim * 2);
+                const uint32_t src = stage_u32 + (n & 1u) * kStageBufBytes;
+                if (n_hg == 1) {
+                    bulk_store(dst, src, (uint32_t)(nt * R * 256));   // the tokens' rows are adjacent at the destination
+                } else {
+                    for (int i = 0; i < nt; ++i) bulk_store(dst + (long long)i * hpr * 256, src + i * R * 256, R * 256);
+                }
+                bulk_commit();
+            }
         }
-        __syncwarp();
+        if (!ok) break;
         if (lane == 0) {
-            __threadfence_system();            // this warp's stores, wherever they went, before the count
+            bulk_wait<0>();                    // this chunk's rows are written, wherever they went
+            fence_proxy_async_all();
+            __threadfence_system();
             atomicAdd_system(x.tile_words[dst_rank] + kind * n_tiles + tok0 / kTileM, 1u);
         }
+        __syncwarp();
     }
+    if (!ok) {
+        // Leaving early: the loads of the buffer that was being filled ahead may still be on their way.
+        volatile uint32_t never = 0;
+        mbar_wait(bar0 + (fills & 1u) * 8, (fills >> 1) & 1u, &never, 40000000ll);
+    }
+    if (lane == 0) bulk_wait<0>();             // nothing of this warp reads shared memory after the kernel's exit
+    return ok;
 }
 
 }  // namespace
@@ -238,7 +296,9 @@ attn_fwd_sm100_kernel(const __grid_constant__ AttnParams p) {
             mbar_init(smem_u32(&ctl->kv_empty[i]), 1);
         }
         mbar_init(smem_u32(&ctl->drain), 1);
+        for (int i = 0; i < 4; ++i) mbar_init(smem_u32(&ctl->xchg_full[0][0]) + i * 8, 1);
         ctl->abort = 0;
+        ctl->softmax_done = 0;
         fence_mbar_init();
         fence_proxy_async_smem();
     }
@@ -326,7 +386,14 @@ attn_fwd_sm100_kernel(const __grid_constant__ AttnParams p) {
             }
         } else if (warp > kMmaWarp) {
             // ------------------------------ head exchange -----------------------------
-            if (p.xchg.enabled) exchange_role(p.xchg, lane);
+            if (p.xchg.enabled) {
+                const int xw = warp - kMmaWarp - 1;
+                const unsigned int cta_linear = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+                exchange_role(p.xchg, lane, smem + kSmemStage + xw * 2 * kStageBufBytes,
+                              smem_raw + (smem - raw_addr) + kSmemStage + xw * 2 * kStageBufBytes,
+                              smem_u32(&ctl->xchg_full[xw][0]), abort_flag, wait_limit, &ctl->softmax_done,
+                              cta_linear + p.xchg.n_sms < gridDim.x * gridDim.y * gridDim.z);
+            }
         } else if (warp == kMmaWarp) {
             // ------------------------------ MMA issuer --------------------------------
             // The whole warp runs this loop converged; umma_* elect one lane per instruction.
@@ -546,6 +613,8 @@ attn_fwd_sm100_kernel(const __grid_constant__ AttnParams p) {
             }
         }
     }
+
+    if (warp < 8 && lane == 0) atomicAdd(&ctl->softmax_done, 1u);   // (also when the warp left its loop early)
 
     // ------------------------------ common exit ---------------------------------
     __syncwarp();

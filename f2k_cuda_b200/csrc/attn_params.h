@@ -56,6 +56,9 @@ struct ExchangeParams {
     unsigned int*  tile_words[8];                   // destination's counters for this source: [Q | KV][tiles]
     unsigned int*  next_chunk;                      // local, zero before the launch
     int   s_loc, n_heads_total, heads_per_rank, world, rank;
+    int   unit_rows;        // head rows of one token moved by one bulk copy: the largest divisor of heads_per_rank <= 16
+    int   tokens_per_buf;   // tokens per staging buffer: min(4, 16 / unit_rows)
+    unsigned int n_sms;     // CTAs that run at a time (one per SM)
     int   enabled;
     float eps;
 };

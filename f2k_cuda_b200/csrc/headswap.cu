@@ -41,7 +41,9 @@
 
 #include "attn_launch.h"
 
+#include <algorithm>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <string>
@@ -366,6 +368,13 @@ int f2k_hx_forward(f2k_hx* h, const void* q_raw, const void* k_raw, const void* 
         }
         x.next_chunk = h->next_chunk();
         x.s_loc = c.seq_local; x.n_heads_total = c.n_heads; x.heads_per_rank = h->hpr; x.world = c.world; x.rank = c.rank;
+        x.unit_rows = 1;
+        for (int r = 2; r <= 16; ++r)
+            if (h->hpr % r == 0) x.unit_rows = r;
+        x.tokens_per_buf = std::min(4, 16 / x.unit_rows);
+        int sms = 148, dev = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        x.n_sms = (unsigned int)sms;
         x.enabled = 1;
         h->have_fparams[set] = true;
     }

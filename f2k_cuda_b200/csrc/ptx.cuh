@@ -137,6 +137,30 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst_smem, const void* tmap,
         : "memory");
 }
 
+// Untiled bulk copies (no multicast): global -> this CTA's shared memory with completion on an
+// mbarrier, and shared -> global (this GPU's memory or a peer's) tracked by the issuing thread's
+// bulk groups. Addresses 16-byte aligned, sizes multiples of 16 bytes.
+__device__ __forceinline__ void bulk_load(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void bulk_store(void* dst, uint32_t src_smem, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                 ::"l"(dst), "r"(src_smem), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// until at most kPending of this thread's bulk groups still have to READ their shared-memory source
+template <int kPending>
+__device__ __forceinline__ void bulk_wait_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kPending) : "memory");
+}
+// until at most kPending of this thread's bulk groups are incomplete (their writes performed)
+template <int kPending>
+__device__ __forceinline__ void bulk_wait() {
+    asm volatile("cp.async.bulk.wait_group %0;" ::"n"(kPending) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
 // ----------------------------------------------------------------------------
 // Tensor memory
 // ----------------------------------------------------------------------------
