@@ -37,6 +37,10 @@ ROOT = Path(__file__).resolve().parent
 if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 
+# The head exchange drives one copy stream per destination rank; each needs a hardware queue of its
+# own (see f2k_hx_exchange_in_copy). Has to be in the environment before CUDA is initialised.
+os.environ.setdefault("CUDA_DEVICE_MAX_CONNECTIONS", "32")
+
 import numpy as np  # noqa: E402
 import torch  # noqa: E402
 
@@ -58,12 +62,13 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="s4608",
                     choices=["s4608", "s8704_seqpar", "s16896_seqpar", "s4608_b4_heads", "s8704_heads", "s16896_heads",
-                             "s8704_hx", "s16896_hx", "s8704_hx2k", "s16896_hx2k"],
+                             "s8704_hx", "s16896_hx", "s8704_hx2k", "s16896_hx2k", "s8704_hxfused", "s16896_hxfused"],
                     help="s4608: the headline shape (heads sharded over the GPUs, batch grows with N). *_seqpar: the "
                          "long shapes with the sequence sharded over the GPUs (strong scaling, K/V pulled over NVLink "
                          "under the kernel). *_heads: a fixed job with its 32 heads sharded 32/N per GPU (strong scaling). "
-                         "*_hx: sequence sharded outside, heads sharded inside (head exchange by peer stores from inside "
-                         "the attention kernel); *_hx2k: the same with the exchange as a kernel of its own")
+                         "*_hx: sequence sharded outside, heads sharded inside (head exchange; copy engines deliver under "
+                         "the attention kernel); *_hx2k: the exchange as a scatter kernel of its own; *_hxfused: on the "
+                         "attention kernel's spare warps")
     ap.add_argument("--no-overlap", action="store_true", help="seqpar: start the kernel only after all K/V pulls")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the timed CPU leg")
     ap.add_argument("--no-reference-kernel", action="store_true",
@@ -630,7 +635,7 @@ def setup_seqpar(job, rank, world, overlap=True):
             "keep": sp}
 
 
-def setup_hx(job, rank, world, fused=True):
+def setup_hx(job, rank, world, mode="copy"):
     """Sequence-parallel attention by head exchange, batch 1, 32 heads: every rank owns S/world tokens
     outside and 32/world heads inside. Step = one kernel that normalises + rotates Q, K and scatters
     Q, K, V by head into the peers' memory, the attention kernel (its epilogue stores each output row
@@ -653,8 +658,9 @@ def setup_hx(job, rank, world, fused=True):
 
     def step():
         # one gain pair for the whole sequence (the single-stream block's call)
-        okk = (hx.forward(q_raw, k_raw, v, g[2], g[3], dcos, dsin, 1e-6) if fused else
-               hx.exchange_in(q_raw, k_raw, v, g[2], g[3], dcos, dsin, 1e-6) and hx.attend())
+        a = (q_raw, k_raw, v, g[2], g[3], dcos, dsin, 1e-6)
+        okk = (hx.forward(*a) if mode == "fused" else
+               (hx.exchange_in_copy(*a) if mode == "copy" else hx.exchange_in(*a)) and hx.attend())
         if not okk:
             raise RuntimeError(hx.last_error())
         out[0] = hx.output()
@@ -669,16 +675,18 @@ def setup_hx(job, rank, world, fused=True):
         (r,) = _reference_streams(ref, [(qa, ka, va, g[2], g[3], dc, ds)], 1, H, D)
         return _device_metrics(out[0], r[:, b:e])
 
-    return {"step": step, "status": hx.device_status, "parity": parity, "launches_per_step": 1 if fused else 2,
+    return {"step": step, "status": hx.device_status, "parity": parity, "launches_per_step": 1 if mode == "fused" else 2,
             "flops_total": 4.0 * H * float(S) ** 2 * D,
             "nvlink_bytes_per_gpu_per_step": 4 * (world - 1) * per * (H // world) * D * 2,
             "workload": f"{w.name}: {S} tokens, batch 1, 32 heads, hd128, {per} tokens per GPU outside, "
                         f"{H // world} heads per GPU inside",
-            "step_text": ("ONE kernel: its spare warps do QK-RMSNorm + RoPE + the head scatter into peer memory while "
-                          "its other warps attend to what has arrived; " if fused else
-                          "QK-RMSNorm + RoPE + head scatter into peer memory (one kernel); attention with ") +
-                         "the epilogue storing into the token owner's memory; wait for the peers' rows",
-            "parallelism": f"headswap{world}" + ("" if fused else "_two_kernels"),
+            "step_text": {"fused": "ONE kernel: its spare warps do QK-RMSNorm + RoPE + the head scatter into peer memory "
+                                   "while its other warps attend to what has arrived; ",
+                          "copy": "QK-RMSNorm + RoPE of all heads (one kernel); copy engines deliver every rank's head "
+                                  "columns while the attention kernel runs on what has arrived, local tokens first; ",
+                          "scatter": "QK-RMSNorm + RoPE + head scatter into peer memory (one kernel); then attention; "}[mode] +
+                         "the epilogue stores each output row into the token owner's memory; wait for the peers' rows",
+            "parallelism": f"headswap{world}_" + mode,
             "l2": "Q, K, V, O of a step (%.0f MB per GPU) exceed the 126 MB L2" % (4 * S * (H // world) * D * 2 / 1e6),
             "keep": hx}
 
@@ -687,8 +695,8 @@ def setup_job(job, rank, world, overlap=True):
     kind = job.rsplit("_", 1)[1]
     if kind == "heads":
         return setup_heads(job, rank, world)
-    if kind in ("hx", "hx2k"):
-        return setup_hx(job, rank, world, fused=kind == "hx")
+    if kind in ("hx", "hx2k", "hxfused"):
+        return setup_hx(job, rank, world, mode={"hx": "copy", "hx2k": "scatter", "hxfused": "fused"}[kind])
     return setup_seqpar(job, rank, world, overlap)
 
 
@@ -734,8 +742,8 @@ def run_strong(args, rank, world):
     }
 
 
-STRONG_JOBS = ("s4608_b4_heads", "s16896_heads", "s16896_seqpar", "s16896_hx", "s16896_hx2k", "s8704_heads", "s8704_seqpar",
-               "s8704_hx")
+STRONG_JOBS = ("s4608_b4_heads", "s16896_heads", "s16896_seqpar", "s16896_hx", "s16896_hx2k", "s16896_hxfused", "s8704_heads",
+               "s8704_seqpar", "s8704_hx")
 
 
 def strong_scaling_section(rank, world, min_seconds=0.5):

@@ -100,6 +100,8 @@ def _declare(lib: C.CDLL) -> None:
     lib.f2k_hx_attach.argtypes = [vp, C.POINTER(vp)]
     lib.f2k_hx_exchange_in.restype = i
     lib.f2k_hx_exchange_in.argtypes = [vp] * 8 + [f, vp]
+    lib.f2k_hx_exchange_in_copy.restype = i
+    lib.f2k_hx_exchange_in_copy.argtypes = [vp] * 8 + [f, vp]
     lib.f2k_hx_forward.restype = i
     lib.f2k_hx_forward.argtypes = [vp] * 8 + [f, vp]
     lib.f2k_hx_attend.restype = i

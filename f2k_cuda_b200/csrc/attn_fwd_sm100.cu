@@ -155,7 +155,6 @@ __device__ __forceinline__ void issue_pv_part(uint32_t d_tmem, uint32_t p_tmem, 
 constexpr uint32_t kStageRowBytes = 16 * 256;                 // 16 head rows
 constexpr uint32_t kStageTabBytes = 4 * 512;                  // cos + sin rows of up to 4 tokens
 constexpr uint32_t kStageBufBytes = kStageRowBytes + kStageTabBytes;
-constexpr uint32_t kStageBytes    = 2 * 2 * kStageBufBytes;   // 2 warps x 2 buffers
 
 // The warp stops taking chunks once its CTA's softmax groups are done (`softmax_done` reaches 8) if
 // a later CTA will take the CTA's place (`may_stop`: CTAs start in index order, one per SM): that

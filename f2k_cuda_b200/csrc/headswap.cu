@@ -112,6 +112,14 @@ struct f2k_hx {
     }
     AttnParams fparams[2];                   // fused form, per buffer set
     bool       have_fparams[2] = {false, false};
+    // copy-engine form (f2k_hx_exchange_in_copy): normalised Q and K of all heads staged locally,
+    // one copy stream per destination, and launch parameters with the segments in ring order
+    unsigned char* stage = nullptr;          // [Qn | Kn], each shard_bytes
+    cudaStream_t   copy_stream[8] = {};
+    cudaEvent_t    ev_prologue = nullptr;
+    AttnParams cparams[2];
+    bool       have_cparams[2] = {false, false};
+    bool       copy_mode = false;            // which exchange the pending attend follows
 };
 
 namespace {
@@ -191,6 +199,10 @@ int f2k_hx_create(const f2k_seqpar_config* cfg, f2k_hx** out) {
 void f2k_hx_destroy(f2k_hx* h) {
     if (!h) return;
     if (h->abort_stream) cudaStreamDestroy(h->abort_stream);
+    for (cudaStream_t cs : h->copy_stream)
+        if (cs) { cudaStreamSynchronize(cs); cudaStreamDestroy(cs); }
+    if (h->ev_prologue) cudaEventDestroy(h->ev_prologue);
+    if (h->stage) cudaFree(h->stage);
     if (h->d_status) cudaFree(h->d_status);
     if (h->buf) cudaFree(h->buf);
     delete h;
@@ -214,6 +226,7 @@ int f2k_hx_attach(f2k_hx* h, void* const* peer_bases) {
     }
     h->have_params[0] = h->have_params[1] = false;
     h->have_fparams[0] = h->have_fparams[1] = false;
+    h->have_cparams[0] = h->have_cparams[1] = false;
     return F2K_OK;
 }
 
@@ -254,6 +267,113 @@ int f2k_hx_exchange_in(f2k_hx* h, const void* q_raw, const void* k_raw, const vo
     const cudaError_t e = qkv_scatter_launch(p, static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return fail_cuda(h, "exchange kernel launch", e);
     h->phase = f2k_hx::kExchanged;
+    h->copy_mode = false;
+    return F2K_OK;
+}
+
+// The exchange with the copy engines doing the transfers: one prologue kernel normalises + rotates
+// Q and K of ALL heads into a local staging area; then, per destination rank and on a stream of its
+// own, three strided copies pick the destination's head columns of K, V (straight from the caller's
+// tensor) and Q and put them into the destination's buffers, local or peer, followed by a stream
+// write of the step number into the destination's "arrived" word for this source. Destinations are
+// served nearest consumer first (rank - 1, rank - 2, ...); the rank's own heads go in on the caller's
+// stream. Nothing occupies an SM after that, so the attention kernel, launched by attend() right behind it, runs while the
+// copies are still on their way and waits, per source rank, for what it needs next.
+int f2k_hx_exchange_in_copy(f2k_hx* h, const void* q_raw, const void* k_raw, const void* v, const void* gamma_q,
+                            const void* gamma_k, const float* cos_local, const float* sin_local, float eps,
+                            void* stream) {
+    if (!h || !h->valid) return F2K_ERR_INVALID;
+    if (!q_raw || !k_raw || !v || !gamma_q || !gamma_k || !cos_local || !sin_local)
+        return fail(h, F2K_ERR_INVALID, "null tensor pointer");
+    for (const void* ptr : {q_raw, k_raw, v, gamma_q, gamma_k, static_cast<const void*>(cos_local),
+                            static_cast<const void*>(sin_local)})
+        if ((reinterpret_cast<uintptr_t>(ptr) & 15u) != 0)
+            return fail(h, F2K_ERR_INVALID, "tensor, gain and table pointers must be 16-byte aligned");
+    const f2k_seqpar_config& c = h->cfg;
+    for (int r = 0; r < c.world; ++r)
+        if (!h->peer[r]) return fail(h, F2K_ERR_INVALID, "peers not attached");
+    if (h->phase != f2k_hx::kIdle)
+        return fail(h, F2K_ERR_INVALID, "exchange_in before the previous step's attend and output");
+    cudaError_t e = cudaSuccess;
+    if (!h->stage) {                                   // first use: staging area, streams, event
+        // Every copy stream needs a hardware queue of its own: a copy that shares a queue with the
+        // caller's stream sits behind that stream's wait for the peers' "done" words, while the
+        // peers wait for the copy. The CUDA default is 8 queues per device for all streams of the
+        // process; more have to be asked for before the CUDA context exists.
+        const char* mc = std::getenv("CUDA_DEVICE_MAX_CONNECTIONS");
+        if (c.world > 1 && (!mc || std::atoi(mc) < c.world + 8))
+            return fail(h, F2K_ERR_UNSUPPORTED,
+                        "the copy-engine exchange needs CUDA_DEVICE_MAX_CONNECTIONS >= world + 8 in the environment "
+                        "before CUDA is initialised (one hardware queue per copy stream)");
+        e = cudaMalloc(reinterpret_cast<void**>(&h->stage), 2 * h->shard_bytes);
+        for (int i = 0; i < c.world && e == cudaSuccess; ++i)
+            e = cudaStreamCreateWithFlags(&h->copy_stream[i], cudaStreamNonBlocking);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->ev_prologue, cudaEventDisableTiming);
+        if (e != cudaSuccess) return fail_cuda(h, "copy-engine exchange set-up", e);
+    }
+    h->epoch += 1;
+    const int set = h->epoch & 1;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    unsigned char* qn = h->stage;
+    unsigned char* kn = h->stage + h->shard_bytes;
+    QkPrologueParams pp;
+    std::memset(&pp, 0, sizeof pp);
+    const long long rows = (long long)c.seq_local * c.n_heads;
+    pp.job[0].x = q_raw; pp.job[0].y = qn; pp.job[0].gamma = gamma_q;
+    pp.job[1].x = k_raw; pp.job[1].y = kn; pp.job[1].gamma = gamma_k;
+    for (int j = 0; j < 2; ++j) {
+        pp.job[j].cos_tab = cos_local; pp.job[j].sin_tab = sin_local; pp.job[j].seq = c.seq_local; pp.job[j].rows = rows;
+    }
+    pp.row_start[0] = 0; pp.row_start[1] = rows; pp.row_start[2] = 2 * rows;
+    pp.n_jobs = 2; pp.n_heads = c.n_heads; pp.eps = eps;
+    e = qk_prologue_launch(pp, s);
+    if (e == cudaSuccess) e = cudaEventRecord(h->ev_prologue, s);
+    if (e != cudaSuccess) return fail_cuda(h, "prologue launch", e);
+    const size_t spitch = (size_t)c.n_heads * kHeadDim * 2;        // a token of all heads
+    const size_t width  = (size_t)h->hpr * kHeadDim * 2;           // a token of one rank's heads
+    const size_t seg_bytes = (size_t)c.seq_local * width;
+    // The rank's own heads stay on this GPU and go in on the caller's stream, ahead of the
+    // attention kernel: a same-device strided copy may run as a kernel, and a kernel queued on
+    // another stream would find every SM taken by an attention kernel that waits for it.
+    {
+        QkPrologueParams po;
+        std::memset(&po, 0, sizeof po);
+        const long long own_rows = (long long)c.seq_local * h->hpr;
+        const size_t col = (size_t)c.rank * width;
+        po.job[0].x = static_cast<const unsigned char*>(q_raw) + col; po.job[0].gamma = gamma_q;
+        po.job[0].y = h->part(h->buf, set, 0) + (size_t)c.rank * seg_bytes;
+        po.job[1].x = static_cast<const unsigned char*>(k_raw) + col; po.job[1].gamma = gamma_k;
+        po.job[1].y = h->part(h->buf, set, 1) + (size_t)c.rank * seg_bytes;
+        for (int j = 0; j < 2; ++j) {
+            po.job[j].x_tok_stride = (long long)c.n_heads * kHeadDim;
+            po.job[j].cos_tab = cos_local; po.job[j].sin_tab = sin_local; po.job[j].seq = c.seq_local; po.job[j].rows = own_rows;
+        }
+        po.row_start[0] = 0; po.row_start[1] = own_rows; po.row_start[2] = 2 * own_rows;
+        po.n_jobs = 2; po.n_heads = h->hpr; po.eps = eps;
+        e = qk_prologue_launch(po, s);
+        if (e == cudaSuccess)
+            e = cudaMemcpy2DAsync(h->part(h->buf, set, 2) + (size_t)c.rank * seg_bytes, width,
+                                  static_cast<const unsigned char*>(v) + col, spitch, width, (size_t)c.seq_local,
+                                  cudaMemcpyDeviceToDevice, s);
+        if (e != cudaSuccess) return fail_cuda(h, "own heads", e);
+    }
+    for (int i = 1; i < c.world; ++i) {
+        const int d = (c.rank - i + c.world) % c.world;            // nearest consumer first
+        cudaStream_t cs = h->copy_stream[i];
+        e = cudaStreamWaitEvent(cs, h->ev_prologue, 0);
+        const unsigned char* src[3] = {kn, static_cast<const unsigned char*>(v), qn};
+        const int part_of[3] = {1, 2, 0};
+        for (int t = 0; t < 3 && e == cudaSuccess; ++t)
+            e = cudaMemcpy2DAsync(h->part(h->peer[d], set, part_of[t]) + (size_t)c.rank * seg_bytes, width,
+                                  src[t] + (size_t)d * width, spitch, width, (size_t)c.seq_local,
+                                  cudaMemcpyDeviceToDevice, cs);
+        if (e != cudaSuccess) return fail_cuda(h, "exchange copy", e);
+        if (h->write32(reinterpret_cast<CUstream>(cs), reinterpret_cast<CUdeviceptr>(h->arrived(h->peer[d], set, c.rank)),
+                       h->epoch, 0) != CUDA_SUCCESS)
+            return fail(h, F2K_ERR_CUDA, "cuStreamWriteValue32 failed");
+    }
+    h->phase = f2k_hx::kExchanged;
+    h->copy_mode = true;
     return F2K_OK;
 }
 
@@ -262,29 +382,36 @@ int f2k_hx_attend(f2k_hx* h, void* stream) {
     if (h->phase != f2k_hx::kExchanged) return fail(h, F2K_ERR_INVALID, "attend without exchange_in");
     const f2k_seqpar_config& c = h->cfg;
     const int set = h->epoch & 1;
-    AttnParams& p = h->params[set];
-    if (!h->have_params[set]) {
+    // After the scatter kernel: segment s = the tokens of rank s, and the rank's own rows need no
+    // wait (they come from the kernel just before on the same stream). After the copy-engine
+    // exchange: ring order starting with the rank's own tokens (what is nearest arrives first), and
+    // CTAs numbered head-fastest so that those of the first segments run first.
+    const bool ring = h->copy_mode;
+    AttnParams& p = ring ? h->cparams[set] : h->params[set];
+    bool& have = ring ? h->have_cparams[set] : h->have_params[set];
+    if (!have) {
         std::memset(&p, 0, sizeof p);
         const long long tok_h = (long long)h->hpr * kHeadDim;          // token stride of the head-sharded tensors
         const long long tok_o = (long long)c.n_heads * kHeadDim;       // token stride of the token-sharded output
         const int tiles_per_seg = (c.seq_local + kTileM - 1) / kTileM;
         const size_t seg_bytes = (size_t)c.seq_local * h->hpr * kHeadDim * 2;
-        for (int s = 0; s < c.world; ++s) {                            // segment s = the tokens of rank s
-            if (!encode(h, &p.tm_q[s], h->part(h->buf, set, 0) + s * seg_bytes, c.seq_local, h->hpr, tok_h) ||
-                !encode(h, &p.tm_k[s], h->part(h->buf, set, 1) + s * seg_bytes, c.seq_local, h->hpr, tok_h) ||
-                !encode(h, &p.tm_v[s], h->part(h->buf, set, 2) + s * seg_bytes, c.seq_local, h->hpr, tok_h))
+        for (int s = 0; s < c.world; ++s) {
+            const int src = ring ? (c.rank + s) % c.world : s;         // whose tokens segment s holds
+            if (!encode(h, &p.tm_q[s], h->part(h->buf, set, 0) + src * seg_bytes, c.seq_local, h->hpr, tok_h) ||
+                !encode(h, &p.tm_k[s], h->part(h->buf, set, 1) + src * seg_bytes, c.seq_local, h->hpr, tok_h) ||
+                !encode(h, &p.tm_v[s], h->part(h->buf, set, 2) + src * seg_bytes, c.seq_local, h->hpr, tok_h))
                 return fail(h, F2K_ERR_CUDA, "tensor map failed");
-            // the output rows of segment s go to rank s, into the columns of this rank's heads
-            p.o_ptr[s] = h->part(h->peer[s], set, 3) + (size_t)c.rank * h->hpr * kHeadDim * 2;
+            // the output rows of the segment go to the rank that owns its tokens, into the columns of this rank's heads
+            p.o_ptr[s] = h->part(h->peer[src], set, 3) + (size_t)c.rank * h->hpr * kHeadDim * 2;
             p.o_tok_stride[s]   = tok_o;
             p.o_batch_stride[s] = tok_o * c.seq_local;
             p.q_len[s] = p.kv_len[s] = c.seq_local;
             p.q_tile_start[s] = p.kv_tile_start[s] = s * tiles_per_seg;
-            if (s != c.rank) p.q_ready[s] = p.kv_ready[s] = h->arrived(h->buf, set, s);
-            p.done_flag[s] = h->done(h->peer[s], set, c.rank);
-            p.fail_flag[s] = h->failed(h->peer[s], set, c.rank);
+            if (src != c.rank) p.q_ready[s] = p.kv_ready[s] = h->arrived(h->buf, set, src);
+            p.done_flag[s] = h->done(h->peer[src], set, c.rank);
+            p.fail_flag[s] = h->failed(h->peer[src], set, c.rank);
         }
-        // this rank's own rows come from the kernel just before on the same stream: no wait needed
+        p.grid_head_fastest = ring ? 1 : 0;
         p.q_tile_start[c.world] = p.kv_tile_start[c.world] = c.world * tiles_per_seg;
         p.n_qseg = p.n_kvseg = c.world;
         p.n_q_tiles = p.n_kv_tiles = c.world * tiles_per_seg;
@@ -295,7 +422,7 @@ int f2k_hx_attend(f2k_hx* h, void* stream) {
         p.status = h->d_status;
         p.done_counter = h->counter(1);
         p.n_done = c.world;
-        h->have_params[set] = true;
+        have = true;
     }
     p.kv_ready_value = h->epoch;
     p.done_value = h->epoch;

@@ -107,6 +107,14 @@ class HeadExchangeAttention:
         return lib.f2k_hx_exchange_in(self._h, p(q_raw), p(k_raw), p(v), p(gamma_q), p(gamma_k), p(cos_local),
                                       p(sin_local), eps, self._stream(stream)) == _lib.F2K_OK
 
+    def exchange_in_copy(self, q_raw, k_raw, v, gamma_q, gamma_k, cos_local, sin_local, eps: float, stream=None) -> bool:
+        """exchange_in with the copy engines doing the transfers (one local prologue kernel, then
+        strided copies per destination on streams of the handle): the attention that attend()
+        launches behind it runs while the copies are on their way."""
+        p = lambda t: C.c_void_p(t.data_ptr())  # noqa: E731
+        return lib.f2k_hx_exchange_in_copy(self._h, p(q_raw), p(k_raw), p(v), p(gamma_q), p(gamma_k), p(cos_local),
+                                           p(sin_local), eps, self._stream(stream)) == _lib.F2K_OK
+
     def forward(self, q_raw, k_raw, v, gamma_q, gamma_k, cos_local, sin_local, eps: float, stream=None) -> bool:
         """exchange_in + attend as one kernel (the exchange runs on the attention kernel's spare
         warps and hides under the attention). One process per GPU, or world == 1."""

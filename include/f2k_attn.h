@@ -309,6 +309,19 @@ int f2k_hx_attach(f2k_hx* h, void* const* peer_bases);
 int f2k_hx_exchange_in(f2k_hx* h, const void* q_raw, const void* k_raw, const void* v,
                        const void* gamma_q, const void* gamma_k,
                        const float* cos_local, const float* sin_local, float eps, void* stream);
+/* exchange_in with the COPY ENGINES doing the transfers: one prologue kernel normalises + rotates Q
+ * and K of all heads locally, then strided copies on streams the handle owns deliver every rank's
+ * head columns of K, V and Q, nearest consumer first, each followed by a stream write of the
+ * arrival word. No SM is busy with the exchange, so the attention kernel that f2k_hx_attend
+ * launches right behind it (segments in ring order, local tokens first) runs while the copies are
+ * on their way. Same arguments and call order as exchange_in. Every copy stream needs a hardware
+ * queue of its own (a copy queued behind the caller's stream would wait for the peers while they
+ * wait for it): the process must run with CUDA_DEVICE_MAX_CONNECTIONS >= world + 8, set before CUDA
+ * is initialised, or the call is refused with F2K_ERR_UNSUPPORTED. Several ranks on ONE GPU (the
+ * tests' emulation): call it for every rank before the first attend. */
+int f2k_hx_exchange_in_copy(f2k_hx* h, const void* q_raw, const void* k_raw, const void* v,
+                            const void* gamma_q, const void* gamma_k,
+                            const float* cos_local, const float* sin_local, float eps, void* stream);
 int f2k_hx_attend(f2k_hx* h, void* stream);
 /* exchange_in and attend as ONE kernel: the attention kernel's spare warps do the exchange (same
  * arithmetic, same peer stores) while its other warps already attend to what has arrived, local

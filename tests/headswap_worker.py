@@ -40,17 +40,21 @@ def main():
                                              tables=(None, None, cos, sin), eps=1e-6)
     dist.barrier()
     # back to back: no collective, no host synchronisation between steps. Steps 0-3 run the exchange
-    # as a kernel of its own, steps 4-7 inside the attention kernel (the fused form).
-    for step in range(8):
+    # as a kernel of its own, steps 4-7 inside the attention kernel (the fused form), steps 8-11 with
+    # the copy engines under the attention kernel.
+    for step in range(12):
         if step < 4:
             assert hx.exchange_in(q, k, v, gq, gk, dcos, dsin, 1e-6), hx.last_error()
             assert hx.attend(), hx.last_error()
-        else:
+        elif step < 8:
             assert hx.forward(q, k, v, gq, gk, dcos, dsin, 1e-6), hx.last_error()
+        else:
+            assert hx.exchange_in_copy(q, k, v, gq, gk, dcos, dsin, 1e-6), hx.last_error()
+            assert hx.attend(), hx.last_error()
         o = hx.output()
         assert o is not None, hx.last_error()
         got = o.clone()                          # stream order: after the waits of output()
-        if step in (0, 3, 4, 7):
+        if step in (0, 3, 4, 7, 8, 11):
             torch.cuda.synchronize()
             assert hx.device_status() == 0, hx.last_error()
             assert_parity(host_f32(got), ref[:, sl], f"rank {rank} step {step}")

@@ -33,9 +33,10 @@ def reference_output(orc, w, p):
 
 # (world, tokens per rank, heads): ragged shards (200, 136: not multiples of 128), an odd number of
 # tiles per shard, one head per rank, world 1
+@pytest.mark.parametrize("copy_engines", [False, True])
 @pytest.mark.parametrize("world,per,H", [(2, 256, 4), (4, 200, 4), (8, 136, 8), (4, 128, 8), (1, 300, 2), (2, 384, 8)])
 @pytest.mark.timeout(120, method="thread")
-def test_all_ranks_in_one_process(orc, world, per, H):
+def test_all_ranks_in_one_process(orc, world, per, H, copy_engines):
     import torch
     from f2k_cuda_b200.headswap import HeadExchangeAttention
     from f2k_cuda_b200.inputs import Workload, make_problem
@@ -54,10 +55,13 @@ def test_all_ranks_in_one_process(orc, world, per, H):
     dcos, dsin = torch.from_numpy(cos).cuda(), torch.from_numpy(sin).cuda()
     shard = lambda x, r: dev_bf16(np.ascontiguousarray(x[:, r * per:(r + 1) * per]))  # noqa: E731
     for step in range(3):                           # both buffer sets, then the first again
+        keep = []                                   # the copy engines read the inputs after the call returns
         for r, hx in enumerate(ranks):
-            assert hx.exchange_in(shard(p.q_img, r), shard(p.k_img, r), shard(p.v_img, r), gq, gk,
-                                  dcos[r * per:(r + 1) * per].contiguous(), dsin[r * per:(r + 1) * per].contiguous(),
-                                  1e-6), hx.last_error()
+            args = (shard(p.q_img, r), shard(p.k_img, r), shard(p.v_img, r), gq, gk,
+                    dcos[r * per:(r + 1) * per].contiguous(), dsin[r * per:(r + 1) * per].contiguous(), 1e-6)
+            keep.append(args)
+            # the exchange as a scatter kernel, or as a prologue kernel + copy-engine transfers
+            assert (hx.exchange_in_copy if copy_engines else hx.exchange_in)(*args), hx.last_error()
         torch.cuda.synchronize()                    # all exchanges done before any attention starts
         for hx in ranks:
             assert hx.attend(), hx.last_error()
