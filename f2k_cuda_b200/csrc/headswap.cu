@@ -36,6 +36,11 @@
 // run this form side by side (a rank's kernel fills the GPU and would wait for a kernel that
 // cannot start), so the in-process emulation of the tests uses the two-kernel form; the fused form
 // is tested with world 1 on one GPU and with one process per GPU.
+//
+// Copy-engine form (f2k_hx_exchange_in_copy, then attend): step 1 is a local prologue kernel plus
+// strided copies by the copy engines, which need no SM: the attention kernel of step 2 is launched
+// right behind the prologue and overlaps the transfers (segments in ring order, the rank's own
+// heads put in place on the caller's stream). See the comment at the function.
 
 #include "f2k_attn.h"
 
