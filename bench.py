@@ -78,6 +78,8 @@ def parse_args():
     ap.add_argument("--sustained-seconds", type=float, default=2.5)
     ap.add_argument("--skip-strong-scaling", action="store_true",
                     help="N > 1: skip the fixed jobs (heads / sequence / head exchange) after the headline legs")
+    ap.add_argument("--strong-jobs", default="",
+                    help="comma-separated subset of the strong-scaling jobs to run (default: all)")
     ap.add_argument("--skip-e2e", action="store_true",
                     help="skip the host-buffer leg (for short profiler captures; the line then has e2e null)")
     return ap.parse_args()
@@ -410,7 +412,7 @@ def run_ours(args, rank, world):
                                             St, Si, D)
         watchdog.start()
         try:
-            strong = strong_scaling_section(rank, world)
+            strong = strong_scaling_section(rank, world, only=tuple(x for x in args.strong_jobs.split(",") if x))
         except Exception as exc:
             strong = {"error": f"{type(exc).__name__}: {exc}"}
         watchdog.cancel()
@@ -746,7 +748,7 @@ STRONG_JOBS = ("s4608_b4_heads", "s16896_heads", "s16896_seqpar", "s16896_hx", "
                "s8704_seqpar", "s8704_hx")
 
 
-def strong_scaling_section(rank, world, min_seconds=0.5):
+def strong_scaling_section(rank, world, min_seconds=0.5, only=()):
     """The fixed jobs the north star names, spread over the `world` GPUs of this run three ways
     (heads, sequence, head exchange), each beside rank 0's own one-GPU time of the same job taken in
     this same run: efficiency = t1 / (world * t_world). Every timed region lasts at least
@@ -763,8 +765,9 @@ def strong_scaling_section(rank, world, min_seconds=0.5):
 
     # rank 0 alone: the whole job on one GPU (the other ranks wait at the barrier inside time_job of the next job)
     t1 = {}
+    jobs = [j for j in STRONG_JOBS if not only or j in only]
     for shape in ("s4608_b4", "s16896", "s8704"):
-        if rank == 0:
+        if rank == 0 and any(j.startswith(shape + "_") for j in jobs):
             j = setup_heads(shape + "_heads", 0, 1)
             steps = n_steps(j["flops_total"])
             ms, clocks = time_job(j, steps, 3, 0, 1)
@@ -773,7 +776,7 @@ def strong_scaling_section(rank, world, min_seconds=0.5):
                                      "clocks": clocks}
             del j
             torch.cuda.empty_cache()
-    for job in STRONG_JOBS:
+    for job in jobs:
         rec = {}
         try:
             j = setup_job(job, rank, world)

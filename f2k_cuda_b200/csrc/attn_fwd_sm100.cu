@@ -589,26 +589,39 @@ attn_fwd_sm100_kernel(const __grid_constant__ AttnParams p) {
             locate_tile<kMaxQSeg>(p.q_tile_start, p.q_len, p.n_qseg, qt, seg, row0, valid);
             const int r = (warp & 3) * 32 + lane;  // row inside the tile
             const float inv = 1.0f / (l_sum + 1e-30f);
-            __nv_bfloat16* orow = static_cast<__nv_bfloat16*>(p.o_ptr[seg]) +
-                                  (long long)bidx * p.o_batch_stride[seg] +
-                                  (long long)(row0 + r) * p.o_tok_stride[seg] +
-                                  (long long)head * kHeadDim;
+            // The rows go out through the shared memory of this tile's Q (no MMA reads it any more:
+            // o_full was committed after the last of them). Each thread parks its row there, 16-byte
+            // chunk c of row r at chunk position c ^ (r & 15), and the warp then writes its 32 rows
+            // two at a time, 16 lanes on the 256 contiguous bytes of one row. To local memory this
+            // saves partial-sector writes; to a peer's memory (head exchange) it turns 16-byte
+            // packets into 256-byte ones.
+            const uint32_t park = smem + kSmemQ + t * kTileBytes;
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
                 uint32_t o[32];
                 tmem_ld_x32(tO + q * 32, o);  // every lane takes part, valid row or not
                 tmem_wait_ld();
-                if (r < valid) {
 #pragma unroll
-                    for (int i = 0; i < 32; i += 8) {
-                        uint4 v;
-                        v.x = pack_bf16x2(__uint_as_float(o[i + 0]) * inv, __uint_as_float(o[i + 1]) * inv);
-                        v.y = pack_bf16x2(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
-                        v.z = pack_bf16x2(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
-                        v.w = pack_bf16x2(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
-                        *reinterpret_cast<uint4*>(orow + q * 32 + i) = v;
-                    }
+                for (int i = 0; i < 32; i += 8) {
+                    uint4 v;
+                    v.x = pack_bf16x2(__uint_as_float(o[i + 0]) * inv, __uint_as_float(o[i + 1]) * inv);
+                    v.y = pack_bf16x2(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
+                    v.z = pack_bf16x2(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
+                    v.w = pack_bf16x2(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
+                    const int c = q * 4 + (i >> 3);
+                    st_shared_v4(park + r * 256 + ((c ^ (r & 15)) << 4), v);
                 }
+            }
+            __syncwarp();
+            __nv_bfloat16* obase = static_cast<__nv_bfloat16*>(p.o_ptr[seg]) +
+                                   (long long)bidx * p.o_batch_stride[seg] + (long long)head * kHeadDim;
+            const int c = lane & 15;
+#pragma unroll 2
+            for (int it = 0; it < 16; ++it) {
+                const int row = (warp & 3) * 32 + it * 2 + (lane >> 4);
+                const uint4 v = ld_shared_v4(park + row * 256 + ((c ^ (row & 15)) << 4));
+                if (row < valid)
+                    *reinterpret_cast<uint4*>(obase + (long long)(row0 + row) * p.o_tok_stride[seg] + c * 8) = v;
             }
         }
     }

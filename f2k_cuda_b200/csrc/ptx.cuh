@@ -137,6 +137,16 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst_smem, const void* tmap,
         : "memory");
 }
 
+// 16-byte accesses to shared memory by shared-space address.
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, const uint4& v) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+    return v;
+}
+
 // Untiled bulk copies (no multicast): global -> this CTA's shared memory with completion on an
 // mbarrier, and shared -> global (this GPU's memory or a peer's) tracked by the issuing thread's
 // bulk groups. Addresses 16-byte aligned, sizes multiples of 16 bytes.
