@@ -142,9 +142,10 @@ __device__ __forceinline__ void issue_pv_part(uint32_t d_tmem, uint32_t p_tmem, 
     }
 }
 
-// Head exchange by one of the CTA's two spare warps (see ExchangeParams). Chunk c of the queue:
-// destination order c / (2 n_sub) (0 = this rank itself, then rank - 1, rank - 2, ...: the order in
-// which the destinations get to this rank's segment), then token block, then Q before K+V.
+// Head exchange by one of the CTA's two spare warps (see ExchangeParams). A chunk is 16 tokens of
+// Q, or of K and V, for one destination. The queue walks the ranges of ExchangeParams::order: ring
+// step i sends to rank - i (0 = this rank itself), which is the order in which the destinations
+// get to this rank's segment.
 //
 // Two warps per CTA cannot keep enough loads in flight from registers (measured: 86 GB/s per
 // GPU), so the rows travel as bulk copies through a small staging area in shared memory: one lane
@@ -165,61 +166,73 @@ __device__ __forceinline__ bool exchange_role(const ExchangeParams& x, int lane,
                                               uint32_t bar0, volatile uint32_t* abort_flag, long long wait_limit,
                                               volatile uint32_t* softmax_done, bool may_stop) {
     const int hl = lane & 15, hw = lane >> 4;
-    const int n_sub = (x.s_loc + kExchangeTokens - 1) / kExchangeTokens;
     const int n_tiles = (x.s_loc + kTileM - 1) / kTileM;
-    const unsigned int per_dest = 2u * n_sub, total = per_dest * x.world;
     const int hpr = x.heads_per_rank, R = x.unit_rows, tpb = x.tokens_per_buf;
     const int n_hg = hpr / R;
     unsigned int fills = 0;                                    // buffers filled so far by this warp: buffer and parity
     bool ok = true;
-    for (;;) {
+
+    struct Chunk { int dst_rank, kind, tok0, tok1, n_tb, per_pass, n_fill; bool valid; };
+    // Next chunk of the queue. The queue is a list of ranges (x.order): what the CTAs that run first
+    // need first - their own query rows - comes first, then K/V in the order the kernel walks them.
+    auto grab = [&]() {
+        Chunk ch;
         unsigned int c = 0xffffffffu;
         if (lane == 0 && !(may_stop && *softmax_done >= 8u)) c = atomicAdd(x.next_chunk, 1u);
         c = __shfl_sync(0xffffffffu, c, 0);
-        if (c >= total) break;
-        const int dst_rank = (x.rank - (int)(c / per_dest) + x.world) % x.world;
-        const unsigned int r = c % per_dest;
-        const int kind = (int)(r & 1u);                       // 0: Q rows, 1: K and V rows
-        const int tok0 = (int)(r >> 1) * kExchangeTokens;
-        const int tok1 = min(tok0 + kExchangeTokens, x.s_loc);
-        const int n_tb = (tok1 - tok0 + tpb - 1) / tpb;
-        const int per_pass = n_hg * n_tb, n_fill = (kind + 1) * per_pass;
-
-        // fill f of the chunk: tensor, head group, token block
-        auto issue = [&](int f) {                              // lane 0 only
-            const int pass = f / per_pass, rem = f % per_pass, hg = rem / n_tb, t0 = tok0 + (rem % n_tb) * tpb;
-            const int nt = min(tpb, tok1 - t0);
-            const bool rot = !(kind == 1 && pass == 1);
-            const __nv_bfloat16* xin = static_cast<const __nv_bfloat16*>(kind == 0 ? x.q : (pass == 0 ? x.k : x.v));
-            const unsigned int n = fills;
-            const uint32_t buf = stage_u32 + (n & 1u) * kStageBufBytes, bar = bar0 + (n & 1u) * 8;
-            bulk_wait_read<0>();                               // the store that last used this buffer has read it
-            mbar_arrive_expect_tx(bar, (uint32_t)nt * (uint32_t)(R * 256 + (rot ? 512 : 0)));
-            for (int i = 0; i < nt; ++i) {
-                bulk_load(buf + i * R * 256, xin + ((long long)(t0 + i) * x.n_heads_total + dst_rank * hpr + hg * R) * kHeadDim,
-                          R * 256, bar);
-                if (rot) {
-                    bulk_load(buf + kStageRowBytes + i * 512, x.cos_tab + (long long)(t0 + i) * 64, 256, bar);
-                    bulk_load(buf + kStageRowBytes + i * 512 + 256, x.sin_tab + (long long)(t0 + i) * 64, 256, bar);
-                }
+        ch.valid = c < x.total_chunks;
+        if (!ch.valid) return ch;
+        int e = 0;
+        unsigned int first = 0;
+        while (e + 1 < x.n_ranges && c >= first + (unsigned int)x.order[e].n) { first += (unsigned int)x.order[e].n; ++e; }
+        ch.kind = x.order[e].kind;                             // 0: Q rows, 1: K and V rows
+        ch.dst_rank = (x.rank - (int)x.order[e].step + x.world) % x.world;
+        ch.tok0 = (x.order[e].sub0 + (int)(c - first)) * kExchangeTokens;
+        ch.tok1 = min(ch.tok0 + kExchangeTokens, x.s_loc);
+        ch.n_tb = (ch.tok1 - ch.tok0 + tpb - 1) / tpb;
+        ch.per_pass = n_hg * ch.n_tb;
+        ch.n_fill = (ch.kind + 1) * ch.per_pass;
+        return ch;
+    };
+    // fill f of a chunk: tensor, head group, token block
+    auto issue = [&](const Chunk& ch, int f) {                 // lane 0 only
+        const int pass = f / ch.per_pass, rem = f % ch.per_pass, hg = rem / ch.n_tb, t0 = ch.tok0 + (rem % ch.n_tb) * tpb;
+        const int nt = min(tpb, ch.tok1 - t0);
+        const bool rot = !(ch.kind == 1 && pass == 1);
+        const __nv_bfloat16* xin = static_cast<const __nv_bfloat16*>(ch.kind == 0 ? x.q : (pass == 0 ? x.k : x.v));
+        const unsigned int n = fills;
+        const uint32_t buf = stage_u32 + (n & 1u) * kStageBufBytes, bar = bar0 + (n & 1u) * 8;
+        bulk_wait_read<0>();                                   // the store that last used this buffer has read it
+        mbar_arrive_expect_tx(bar, (uint32_t)nt * (uint32_t)(R * 256 + (rot ? 512 : 0)));
+        for (int i = 0; i < nt; ++i) {
+            bulk_load(buf + i * R * 256, xin + ((long long)(t0 + i) * x.n_heads_total + ch.dst_rank * hpr + hg * R) * kHeadDim,
+                      R * 256, bar);
+            if (rot) {
+                bulk_load(buf + kStageRowBytes + i * 512, x.cos_tab + (long long)(t0 + i) * 64, 256, bar);
+                bulk_load(buf + kStageRowBytes + i * 512 + 256, x.sin_tab + (long long)(t0 + i) * 64, 256, bar);
             }
-        };
-        if (lane == 0) issue(0);
-        for (int f = 0; f < n_fill; ++f) {
+        }
+    };
+
+    Chunk cur = grab();
+    if (cur.valid && lane == 0) issue(cur, 0);
+    while (cur.valid) {
+        for (int f = 0; f < cur.n_fill; ++f) {
             const unsigned int n = fills;                      // the buffer fill f went into
             ++fills;
-            if (f + 1 < n_fill && lane == 0) issue(f + 1);
+            if (f + 1 < cur.n_fill && lane == 0) issue(cur, f + 1);
             __syncwarp();
             ok = mbar_wait(bar0 + (n & 1u) * 8, (n >> 1) & 1u, abort_flag, wait_limit);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
-            const int pass = f / per_pass, rem = f % per_pass, hg = rem / n_tb, t0 = tok0 + (rem % n_tb) * tpb;
-            const int nt = min(tpb, tok1 - t0);
-            const bool rot = !(kind == 1 && pass == 1);
+            const int pass = f / cur.per_pass, rem = f % cur.per_pass, hg = rem / cur.n_tb;
+            const int t0 = cur.tok0 + (rem % cur.n_tb) * tpb;
+            const int nt = min(tpb, cur.tok1 - t0);
+            const bool rot = !(cur.kind == 1 && pass == 1);
             uint8_t* buf = stage_ptr + (n & 1u) * kStageBufBytes;
             if (rot) {
                 float g[8];
-                unpack8(__ldg(reinterpret_cast<const uint4*>(kind == 0 ? x.gamma_q : x.gamma_k) + hl), g);
+                unpack8(__ldg(reinterpret_cast<const uint4*>(cur.kind == 0 ? x.gamma_q : x.gamma_k) + hl), g);
                 for (int row = hw; row < nt * R; row += 2) {   // a half-warp per row; both halves run the same count
                     const int ti = row / R;
                     uint4* cell = reinterpret_cast<uint4*>(buf + row * 256) + hl;
@@ -232,7 +245,8 @@ __device__ __forceinline__ bool exchange_role(const ExchangeParams& x, int lane,
             }
             __syncwarp();
             if (lane == 0) {
-                unsigned char* base = kind == 0 ? x.dst_q[dst_rank] : (pass == 0 ? x.dst_k[dst_rank] : x.dst_v[dst_rank]);
+                unsigned char* base = cur.kind == 0 ? x.dst_q[cur.dst_rank]
+                                                    : (pass == 0 ? x.dst_k[cur.dst_rank] : x.dst_v[cur.dst_rank]);
                 unsigned char* dst = base + (((long long)x.rank * x.s_loc + t0) * hpr + hg * R) * (long long)(kHeadDim * 2);
                 const uint32_t src = stage_u32 + (n & 1u) * kStageBufBytes;
                 if (n_hg == 1) {
@@ -244,13 +258,23 @@ __device__ __forceinline__ bool exchange_role(const ExchangeParams& x, int lane,
             }
         }
         if (!ok) break;
+        // The first loads of the next chunk are started before this chunk's stores are waited for.
+        const Chunk nxt = grab();
+        if (nxt.valid && lane == 0) issue(nxt, 0);
         if (lane == 0) {
             bulk_wait<0>();                    // this chunk's rows are written, wherever they went
             fence_proxy_async_all();
             __threadfence_system();
-            atomicAdd_system(x.tile_words[dst_rank] + kind * n_tiles + tok0 / kTileM, 1u);
+            unsigned int* word = x.tile_words[cur.dst_rank] + cur.kind * n_tiles + cur.tok0 / kTileM;
+            if (cur.kind == 1 && x.kv_walk_words[cur.dst_rank] != nullptr) {
+                const int g = x.rank * x.s_loc + cur.tok0, start = cur.dst_rank * x.s_loc;
+                const int tiles_a = (x.world * x.s_loc - start + kTileN - 1) / kTileN;
+                word = x.kv_walk_words[cur.dst_rank] + (g >= start ? (g - start) / kTileN : tiles_a + g / kTileN);
+            }
+            atomicAdd_system(word, 1u);
         }
         __syncwarp();
+        cur = nxt;
     }
     if (!ok) {
         // Leaving early: the loads of the buffer that was being filled ahead may still be on their way.
@@ -354,8 +378,9 @@ attn_fwd_sm100_kernel(const __grid_constant__ AttnParams p) {
                     } else if (row0 == 0 && p.kv_ready[seg] != nullptr) {
                         // first tile of a segment that is being copied in: wait for its arrival word,
                         // then order the copy engine's writes before this thread's TMA reads
-                        ok = global_flag_wait(p.kv_ready[seg] + head / max(1, p.kv_ready_heads_per_group),
-                                              p.kv_ready_value, abort_flag, peer_limit);
+                        const unsigned int* word = p.kv_ready[seg] + head / max(1, p.kv_ready_heads_per_group);
+                        for (int i = 0; i < max(1, p.kv_ready_words) && ok; ++i)
+                            ok = global_flag_wait(word + i, p.kv_ready_value, abort_flag, peer_limit);
                         if (!ok) break;
                         asm volatile("fence.proxy.async.global;" ::: "memory");
                     }

@@ -48,13 +48,26 @@ constexpr long long kDefaultPeerWaitClk = 40000000000ll;   // ~20 s
 // TMA producer waits until a tile's counter has reached (number of steps so far) x (chunks of the
 // tile). Only CTAs that are running take chunks, so no CTA ever waits for work held by a CTA that
 // has not started.
+// A run of chunks of the exchange queue: sub-blocks sub0 .. sub0 + n - 1 (16 tokens each) of
+// kind 0 (Q) or 1 (K and V), sent at ring step `step` (to rank - step).
+struct ExchangeRange { short kind, step; int sub0, n; };
+constexpr int kMaxExchangeRanges = 32;
+
 struct ExchangeParams {
     const void*  q; const void* k; const void* v;   // [s_loc, n_heads_total, 128] bf16, dense
     const void*  gamma_q; const void* gamma_k;      // [128] bf16
     const float* cos_tab; const float* sin_tab;     // [s_loc, 64] fp32: this rank's rows
     unsigned char* dst_q[8]; unsigned char* dst_k[8]; unsigned char* dst_v[8];   // per destination rank
     unsigned int*  tile_words[8];                   // destination's counters for this source: [Q | KV][tiles]
+    // When not null: the destination walks K/V as at most two segments of its buffer, tokens
+    // [start, world * s_loc) then [0, start) with start = destination * s_loc, and has one counter
+    // per 128-token tile of that walk, shared by all sources (s_loc is a multiple of 16 then, so a
+    // chunk never straddles two tiles). K/V chunks count there instead of tile_words.
+    unsigned int*  kv_walk_words[8];
     unsigned int*  next_chunk;                      // local, zero before the launch
+    ExchangeRange  order[kMaxExchangeRanges];       // the queue, in the order the attention needs the rows
+    int            n_ranges;
+    unsigned int   total_chunks;                    // sum of order[].n = 2 * world * ceil(s_loc / 16)
     int   s_loc, n_heads_total, heads_per_rank, world, rank;
     int   unit_rows;        // head rows of one token moved by one bulk copy: the largest divisor of heads_per_rank <= 16
     int   tokens_per_buf;   // tokens per staging buffer: min(4, 16 / unit_rows)
@@ -103,6 +116,9 @@ struct AttnParams {
     const unsigned int* kv_ready[kMaxKvSeg];
     unsigned int        kv_ready_value;
     int                 kv_ready_heads_per_group;
+    // A segment filled by several writers: the producer waits for kv_ready_words consecutive words
+    // starting at the one above (0 or 1 = that word alone).
+    int                 kv_ready_words;
 
     // Per-tile readiness (fused head exchange): when ready_per_tile is set, q_ready[i] / kv_ready[i]
     // point at one counter per 128-token tile of segment i; a tile may be fetched once its counter

@@ -115,6 +115,11 @@ struct f2k_hx {
     unsigned int* tile_words(unsigned char* base, int set, int src) const {   // [Q tiles | KV tiles]
         return reinterpret_cast<unsigned int*>(base + flags_off + kControlBytes) + ((size_t)set * cfg.world + src) * 2 * n_tiles;
     }
+    // fused form, K/V walked as two segments of the whole buffer: one counter per tile of the walk
+    // and buffer set, shared by all sources (behind the per-source counters)
+    unsigned int* walk_words(unsigned char* base, int set) const {
+        return tile_words(base, 2, 0) + (size_t)set * cfg.world * n_tiles;
+    }
     AttnParams fparams[2];                   // fused form, per buffer set
     bool       have_fparams[2] = {false, false};
     // copy-engine form (f2k_hx_exchange_in_copy): normalised Q and K of all heads staged locally,
@@ -171,7 +176,7 @@ int f2k_hx_create(const f2k_seqpar_config* cfg, f2k_hx** out) {
     h->flags_off   = 8 * h->shard_bytes;
     h->n_tiles     = (cfg->seq_local + kTileM - 1) / kTileM;
     h->total_bytes = h->flags_off + f2k_hx::kControlBytes +
-                     ((size_t)2 * cfg->world * 2 * h->n_tiles * sizeof(unsigned int) + 255) / 256 * 256;
+                     ((size_t)2 * cfg->world * 3 * h->n_tiles * sizeof(unsigned int) + 255) / 256 * 256;
 
     int dev = 0, major = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -420,6 +425,24 @@ int f2k_hx_attend(f2k_hx* h, void* stream) {
         p.q_tile_start[c.world] = p.kv_tile_start[c.world] = c.world * tiles_per_seg;
         p.n_qseg = p.n_kvseg = c.world;
         p.n_q_tiles = p.n_kv_tiles = c.world * tiles_per_seg;
+        if (!ring && c.world > 1) {
+            // After the scatter kernel all sources arrive at about the same time and the segments
+            // lie back to back in rank order: K/V are walked as ONE segment (no padded tile per
+            // source), once every source's arrival word is there - the rank's own included, its
+            // exchange kernel writes it too.
+            const int all = c.world * c.seq_local;
+            if (!encode(h, &p.tm_k[0], h->part(h->buf, set, 1), all, h->hpr, tok_h) ||
+                !encode(h, &p.tm_v[0], h->part(h->buf, set, 2), all, h->hpr, tok_h))
+                return fail(h, F2K_ERR_CUDA, "tensor map failed");
+            for (int s = 0; s < c.world; ++s) { p.kv_ready[s] = nullptr; p.kv_len[s] = 0; p.kv_tile_start[s + 1] = 0; }
+            p.kv_len[0] = all;
+            p.kv_tile_start[0] = 0;
+            p.kv_tile_start[1] = (all + kTileN - 1) / kTileN;
+            p.n_kvseg = 1;
+            p.n_kv_tiles = p.kv_tile_start[1];
+            p.kv_ready[0] = h->arrived(h->buf, set, 0);
+            p.kv_ready_words = c.world;
+        }
         p.kv_ready_heads_per_group = h->hpr;                            // one word per source rank
         p.n_heads = h->hpr;
         p.batch = 1;
@@ -482,6 +505,32 @@ int f2k_hx_forward(f2k_hx* h, const void* q_raw, const void* k_raw, const void* 
         p.q_tile_start[c.world] = p.kv_tile_start[c.world] = c.world * tiles_per_seg;
         p.n_qseg = p.n_kvseg = c.world;
         p.n_q_tiles = p.n_kv_tiles = c.world * tiles_per_seg;
+        // K/V: the sources' rows lie back to back in rank order, so the ring walk is two pieces of
+        // the whole buffer, tokens [start, end) and [0, start) - one padded tile per piece instead
+        // of one per source. Needs chunks that never straddle a tile of the walk.
+        const bool walk = c.world > 1 && c.seq_local % kExchangeTokens == 0;
+        if (walk) {
+            const int all = c.world * c.seq_local, start = c.rank * c.seq_local;
+            const size_t start_bytes = (size_t)start * h->hpr * kHeadDim * 2;
+            const int len[2] = {all - start, start};
+            const size_t off[2] = {start_bytes, 0};
+            for (int i = 0; i < c.world; ++i) { p.kv_ready[i] = nullptr; p.kv_len[i] = 0; p.kv_tile_start[i + 1] = 0; }
+            int n = 0, tiles = 0;
+            for (int i = 0; i < 2; ++i) {
+                if (len[i] == 0) continue;
+                if (!encode(h, &p.tm_k[n], h->part(h->buf, set, 1) + off[i], len[i], h->hpr, tok_h) ||
+                    !encode(h, &p.tm_v[n], h->part(h->buf, set, 2) + off[i], len[i], h->hpr, tok_h))
+                    return fail(h, F2K_ERR_CUDA, "tensor map failed");
+                p.kv_len[n] = len[i];
+                p.kv_tile_start[n] = tiles;
+                p.kv_ready[n] = h->walk_words(h->buf, set) + tiles;
+                tiles += (len[i] + kTileN - 1) / kTileN;
+                ++n;
+            }
+            p.kv_tile_start[n] = tiles;
+            p.n_kvseg = n;
+            p.n_kv_tiles = tiles;
+        }
         p.kv_ready_heads_per_group = h->hpr;
         p.n_heads = h->hpr;
         p.batch = 1;
@@ -497,6 +546,7 @@ int f2k_hx_forward(f2k_hx* h, const void* q_raw, const void* k_raw, const void* 
             x.dst_k[d] = h->part(h->peer[d], set, 1);
             x.dst_v[d] = h->part(h->peer[d], set, 2);
             x.tile_words[d] = h->tile_words(h->peer[d], set, c.rank);
+            x.kv_walk_words[d] = walk ? h->walk_words(h->peer[d], set) : nullptr;
         }
         x.next_chunk = h->next_chunk();
         x.s_loc = c.seq_local; x.n_heads_total = c.n_heads; x.heads_per_rank = h->hpr; x.world = c.world; x.rank = c.rank;
@@ -507,6 +557,28 @@ int f2k_hx_forward(f2k_hx* h, const void* q_raw, const void* k_raw, const void* 
         int sms = 148, dev = 0;
         if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         x.n_sms = (unsigned int)sms;
+        // The queue. CTAs start in index order, head fastest, so the first `sms` of them hold the
+        // first 2 * ceil(sms / heads) query tiles in ring order: their Q rows go first, then the
+        // K/V of the first two ring steps, then the other Q rows (the CTAs that need them start a
+        // wave later), then K/V step by step - delivery is faster than the kernel's walk.
+        const int n_sub = (c.seq_local + kExchangeTokens - 1) / kExchangeTokens;
+        const int first_tiles = std::min(2 * ((sms + h->hpr - 1) / h->hpr), c.world * tiles_per_seg);
+        x.n_ranges = 0;
+        x.total_chunks = 0;
+        auto add = [&x](int kind, int step, int sub0, int n) {
+            if (n <= 0) return;
+            x.order[x.n_ranges++] = ExchangeRange{(short)kind, (short)step, sub0, n};
+            x.total_chunks += (unsigned int)n;
+        };
+        int q_first[kMaxQSeg];
+        for (int i = 0; i < c.world; ++i) {
+            const int tiles = std::max(0, std::min(tiles_per_seg, first_tiles - i * tiles_per_seg));
+            q_first[i] = std::min(n_sub, tiles * (kTileM / kExchangeTokens));
+            add(0, i, 0, q_first[i]);
+        }
+        for (int i = 0; i < std::min(2, c.world); ++i) add(1, i, 0, n_sub);
+        for (int i = 0; i < c.world; ++i) add(0, i, q_first[i], n_sub - q_first[i]);
+        for (int i = 2; i < c.world; ++i) add(1, i, 0, n_sub);
         x.enabled = 1;
         h->have_fparams[set] = true;
     }
