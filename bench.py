@@ -62,13 +62,13 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="s4608",
                     choices=["s4608", "s8704_seqpar", "s16896_seqpar", "s4608_b4_heads", "s8704_heads", "s16896_heads",
-                             "s8704_hx", "s16896_hx", "s8704_hx2k", "s16896_hx2k", "s8704_hxfused", "s16896_hxfused"],
+                             "s8704_hx", "s16896_hx", "s8704_hxfused", "s16896_hxfused", "s8704_hxce", "s16896_hxce"],
                     help="s4608: the headline shape (heads sharded over the GPUs, batch grows with N). *_seqpar: the "
                          "long shapes with the sequence sharded over the GPUs (strong scaling, K/V pulled over NVLink "
                          "under the kernel). *_heads: a fixed job with its 32 heads sharded 32/N per GPU (strong scaling). "
-                         "*_hx: sequence sharded outside, heads sharded inside (head exchange; copy engines deliver under "
-                         "the attention kernel); *_hx2k: the exchange as a scatter kernel of its own; *_hxfused: on the "
-                         "attention kernel's spare warps")
+                         "*_hx: sequence sharded outside, heads sharded inside (head exchange by a scatter kernel in front "
+                         "of the attention kernel); *_hxfused: the exchange on the attention kernel's spare warps; "
+                         "*_hxce: copy engines deliver under the attention kernel")
     ap.add_argument("--no-overlap", action="store_true", help="seqpar: start the kernel only after all K/V pulls")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the timed CPU leg")
     ap.add_argument("--no-reference-kernel", action="store_true",
@@ -637,12 +637,14 @@ def setup_seqpar(job, rank, world, overlap=True):
             "keep": sp}
 
 
-def setup_hx(job, rank, world, mode="copy"):
+def setup_hx(job, rank, world, mode="scatter"):
     """Sequence-parallel attention by head exchange, batch 1, 32 heads: every rank owns S/world tokens
     outside and 32/world heads inside. Step = one kernel that normalises + rotates Q, K and scatters
     Q, K, V by head into the peers' memory, the attention kernel (its epilogue stores each output row
     into the token owner's memory), and the wait for the other ranks' rows. No collective and no
-    copy engine in the step."""
+    copy engine in the step. mode "fused": the exchange runs on the attention kernel's spare warps
+    (one kernel per step); mode "copy": a prologue kernel, then copy engines deliver the head
+    columns under the attention kernel."""
     from f2k_cuda_b200.headswap import HeadExchangeAttention
     w = _shape_of(job)
     S, H, D = w.seq, w.n_heads, w.head_dim
@@ -677,7 +679,7 @@ def setup_hx(job, rank, world, mode="copy"):
         (r,) = _reference_streams(ref, [(qa, ka, va, g[2], g[3], dc, ds)], 1, H, D)
         return _device_metrics(out[0], r[:, b:e])
 
-    return {"step": step, "status": hx.device_status, "parity": parity, "launches_per_step": 1 if mode == "fused" else 2,
+    return {"step": step, "status": hx.device_status, "parity": parity, "launches_per_step": {"fused": 1, "scatter": 2, "copy": 3}[mode],
             "flops_total": 4.0 * H * float(S) ** 2 * D,
             "nvlink_bytes_per_gpu_per_step": 4 * (world - 1) * per * (H // world) * D * 2,
             "workload": f"{w.name}: {S} tokens, batch 1, 32 heads, hd128, {per} tokens per GPU outside, "
@@ -697,8 +699,8 @@ def setup_job(job, rank, world, overlap=True):
     kind = job.rsplit("_", 1)[1]
     if kind == "heads":
         return setup_heads(job, rank, world)
-    if kind in ("hx", "hx2k", "hxfused"):
-        return setup_hx(job, rank, world, mode={"hx": "copy", "hx2k": "scatter", "hxfused": "fused"}[kind])
+    if kind in ("hx", "hxfused", "hxce"):
+        return setup_hx(job, rank, world, mode={"hx": "scatter", "hxfused": "fused", "hxce": "copy"}[kind])
     return setup_seqpar(job, rank, world, overlap)
 
 
@@ -744,7 +746,7 @@ def run_strong(args, rank, world):
     }
 
 
-STRONG_JOBS = ("s4608_b4_heads", "s16896_heads", "s16896_seqpar", "s16896_hx", "s16896_hx2k", "s16896_hxfused", "s8704_heads",
+STRONG_JOBS = ("s4608_b4_heads", "s16896_heads", "s16896_seqpar", "s16896_hx", "s16896_hxfused", "s16896_hxce", "s8704_heads",
                "s8704_seqpar", "s8704_hx")
 
 
