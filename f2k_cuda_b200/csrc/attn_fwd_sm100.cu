@@ -287,6 +287,9 @@ __device__ __forceinline__ bool exchange_role(const ExchangeParams& x, int lane,
 
 }  // namespace
 
+// kWithExchange: the build of the kernel whose spare warps can run the head exchange (launches
+// with p.xchg.enabled). The plain build has no code, shared memory or barriers for it.
+template <bool kWithExchange>
 __global__ void __launch_bounds__(kThreads, 1)
 attn_fwd_sm100_kernel(const __grid_constant__ AttnParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -319,7 +322,8 @@ attn_fwd_sm100_kernel(const __grid_constant__ AttnParams p) {
             mbar_init(smem_u32(&ctl->kv_empty[i]), 1);
         }
         mbar_init(smem_u32(&ctl->drain), 1);
-        for (int i = 0; i < 4; ++i) mbar_init(smem_u32(&ctl->xchg_full[0][0]) + i * 8, 1);
+        if constexpr (kWithExchange)
+            for (int i = 0; i < 4; ++i) mbar_init(smem_u32(&ctl->xchg_full[0][0]) + i * 8, 1);
         ctl->abort = 0;
         ctl->softmax_done = 0;
         fence_mbar_init();
@@ -410,7 +414,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ AttnParams p) {
             }
         } else if (warp > kMmaWarp) {
             // ------------------------------ head exchange -----------------------------
-            if (p.xchg.enabled) {
+            if constexpr (kWithExchange) if (p.xchg.enabled) {
                 const int xw = warp - kMmaWarp - 1;
                 const unsigned int cta_linear = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
                 exchange_role(p.xchg, lane, smem + kSmemStage + xw * 2 * kStageBufBytes,
@@ -651,7 +655,8 @@ attn_fwd_sm100_kernel(const __grid_constant__ AttnParams p) {
         }
     }
 
-    if (warp < 8 && lane == 0) atomicAdd(&ctl->softmax_done, 1u);   // (also when the warp left its loop early)
+    if constexpr (kWithExchange)
+        if (warp < 8 && lane == 0) atomicAdd(&ctl->softmax_done, 1u);   // (also when the warp left its loop early)
 
     // ------------------------------ common exit ---------------------------------
     __syncwarp();
@@ -668,7 +673,8 @@ attn_fwd_sm100_kernel(const __grid_constant__ AttnParams p) {
     }
 }
 
-size_t attn_fwd_smem_bytes() { return kSmemUsed + 1024; }
+size_t attn_fwd_smem_bytes() { return kSmemStage + 1024; }                        // plain build
+static size_t attn_fwd_smem_bytes_exchange() { return kSmemUsed + 1024; }         // + the exchange's staging area
 
 // Loads the kernel on the current device and raises its shared-memory limit. Called when a
 // handle is created, so that the first launch does not have to load code: loading may
@@ -680,11 +686,16 @@ cudaError_t attn_fwd_prepare() {
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
     if (dev < 64 && configured[dev]) return cudaSuccess;
-    e = cudaFuncSetAttribute(attn_fwd_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    e = cudaFuncSetAttribute(attn_fwd_sm100_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)attn_fwd_smem_bytes());
     if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(attn_fwd_sm100_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)attn_fwd_smem_bytes_exchange());
+    if (e != cudaSuccess) return e;
     cudaFuncAttributes attr;
-    e = cudaFuncGetAttributes(&attr, attn_fwd_sm100_kernel);
+    e = cudaFuncGetAttributes(&attr, attn_fwd_sm100_kernel<false>);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncGetAttributes(&attr, attn_fwd_sm100_kernel<true>);
     if (e != cudaSuccess) return e;
     if (dev < 64) configured[dev] = true;
     return cudaSuccess;
@@ -702,10 +713,12 @@ cudaError_t attn_fwd_launch(const AttnParams& params, cudaStream_t stream) {
     for (int i = 0; i < kMaxKvSeg; ++i) peer_words |= p.kv_ready[i] != nullptr;
     for (int i = 0; i < kMaxQSeg; ++i) peer_words |= p.q_ready[i] != nullptr;
     if (peer_words) p.wait_limit_clk += p.peer_wait_limit_clk;
-    const size_t smem = attn_fwd_smem_bytes();
     dim3 grid((p.n_q_tiles + 1) / 2, p.n_heads, p.batch);
     if (p.grid_head_fastest) grid = dim3(p.n_heads, (p.n_q_tiles + 1) / 2, p.batch);
-    attn_fwd_sm100_kernel<<<grid, kThreads, smem, stream>>>(p);
+    if (p.xchg.enabled)
+        attn_fwd_sm100_kernel<true><<<grid, kThreads, attn_fwd_smem_bytes_exchange(), stream>>>(p);
+    else
+        attn_fwd_sm100_kernel<false><<<grid, kThreads, attn_fwd_smem_bytes(), stream>>>(p);
     return cudaPeekAtLastError();
 }
 
