@@ -267,9 +267,8 @@ __device__ __forceinline__ bool exchange_role(const ExchangeParams& x, int lane,
             __threadfence_system();
             unsigned int* word = x.tile_words[cur.dst_rank] + cur.kind * n_tiles + cur.tok0 / kTileM;
             if (cur.kind == 1 && x.kv_walk_words[cur.dst_rank] != nullptr) {
-                const int g = x.rank * x.s_loc + cur.tok0, start = cur.dst_rank * x.s_loc;
-                const int tiles_a = (x.world * x.s_loc - start + kTileN - 1) / kTileN;
-                word = x.kv_walk_words[cur.dst_rank] + (g >= start ? (g - start) / kTileN : tiles_a + g / kTileN);
+                word = x.kv_walk_words[cur.dst_rank] +
+                       kv_walk_tile(x.rank * x.s_loc + cur.tok0, cur.dst_rank * x.s_loc, x.world * x.s_loc);
             }
             atomicAdd_system(word, 1u);
         }

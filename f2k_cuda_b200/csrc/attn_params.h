@@ -77,6 +77,18 @@ struct ExchangeParams {
 };
 constexpr int kExchangeTokens = 16;   // tokens per chunk: 8 chunks per 128-token tile
 
+#ifdef __CUDACC__
+#define F2K_HOST_DEVICE __host__ __device__
+#else
+#define F2K_HOST_DEVICE
+#endif
+// Tile of a destination's two-piece K/V walk (tokens [start, all) then [0, start)) that token g
+// of the whole sequence falls into: the counter a chunk starting at g counts in.
+F2K_HOST_DEVICE inline int kv_walk_tile(int g, int start, int all) {
+    const int tiles_a = (all - start + kTileN - 1) / kTileN;
+    return g >= start ? (g - start) / kTileN : tiles_a + g / kTileN;
+}
+
 struct AttnParams {
     // 4-D tensor maps, dims (fastest first): head_dim, head, token, batch;
     // box = 64 x 1 x 128 x 1 elements, 128-byte swizzle, zero fill out of bounds.

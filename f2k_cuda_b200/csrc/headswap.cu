@@ -462,6 +462,34 @@ int f2k_hx_attend(f2k_hx* h, void* stream) {
     return F2K_OK;
 }
 
+namespace {
+// The chunk queue of the fused exchange. CTAs start in index order, head fastest, so the first
+// `sms` of them hold the first 2 * ceil(sms / heads) query tiles in ring order: their Q rows go
+// first, then the K/V of the first two ring steps, then the other Q rows (the CTAs that need them
+// start a wave later), then K/V step by step - delivery is faster than the kernel's walk.
+void fill_exchange_order(ExchangeParams& x, int world, int seq_local, int heads_per_rank, int sms) {
+    const int n_sub = (seq_local + kExchangeTokens - 1) / kExchangeTokens;
+    const int tiles_per_seg = (seq_local + kTileM - 1) / kTileM;
+    const int first_tiles = std::min(2 * ((sms + heads_per_rank - 1) / heads_per_rank), world * tiles_per_seg);
+    x.n_ranges = 0;
+    x.total_chunks = 0;
+    auto add = [&x](int kind, int step, int sub0, int n) {
+        if (n <= 0) return;
+        x.order[x.n_ranges++] = ExchangeRange{(short)kind, (short)step, sub0, n};
+        x.total_chunks += (unsigned int)n;
+    };
+    int q_first[kMaxQSeg];
+    for (int i = 0; i < world; ++i) {
+        const int tiles = std::max(0, std::min(tiles_per_seg, first_tiles - i * tiles_per_seg));
+        q_first[i] = std::min(n_sub, tiles * (kTileM / kExchangeTokens));
+        add(0, i, 0, q_first[i]);
+    }
+    for (int i = 0; i < std::min(2, world); ++i) add(1, i, 0, n_sub);
+    for (int i = 0; i < world; ++i) add(0, i, q_first[i], n_sub - q_first[i]);
+    for (int i = 2; i < world; ++i) add(1, i, 0, n_sub);
+}
+}  // namespace
+
 int f2k_hx_forward(f2k_hx* h, const void* q_raw, const void* k_raw, const void* v, const void* gamma_q,
                    const void* gamma_k, const float* cos_local, const float* sin_local, float eps, void* stream) {
     if (!h || !h->valid) return F2K_ERR_INVALID;
@@ -557,28 +585,7 @@ int f2k_hx_forward(f2k_hx* h, const void* q_raw, const void* k_raw, const void* 
         int sms = 148, dev = 0;
         if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         x.n_sms = (unsigned int)sms;
-        // The queue. CTAs start in index order, head fastest, so the first `sms` of them hold the
-        // first 2 * ceil(sms / heads) query tiles in ring order: their Q rows go first, then the
-        // K/V of the first two ring steps, then the other Q rows (the CTAs that need them start a
-        // wave later), then K/V step by step - delivery is faster than the kernel's walk.
-        const int n_sub = (c.seq_local + kExchangeTokens - 1) / kExchangeTokens;
-        const int first_tiles = std::min(2 * ((sms + h->hpr - 1) / h->hpr), c.world * tiles_per_seg);
-        x.n_ranges = 0;
-        x.total_chunks = 0;
-        auto add = [&x](int kind, int step, int sub0, int n) {
-            if (n <= 0) return;
-            x.order[x.n_ranges++] = ExchangeRange{(short)kind, (short)step, sub0, n};
-            x.total_chunks += (unsigned int)n;
-        };
-        int q_first[kMaxQSeg];
-        for (int i = 0; i < c.world; ++i) {
-            const int tiles = std::max(0, std::min(tiles_per_seg, first_tiles - i * tiles_per_seg));
-            q_first[i] = std::min(n_sub, tiles * (kTileM / kExchangeTokens));
-            add(0, i, 0, q_first[i]);
-        }
-        for (int i = 0; i < std::min(2, c.world); ++i) add(1, i, 0, n_sub);
-        for (int i = 0; i < c.world; ++i) add(0, i, q_first[i], n_sub - q_first[i]);
-        for (int i = 2; i < c.world; ++i) add(1, i, 0, n_sub);
+        fill_exchange_order(x, c.world, c.seq_local, h->hpr, sms);
         x.enabled = 1;
         h->have_fparams[set] = true;
     }
@@ -596,6 +603,32 @@ int f2k_hx_forward(f2k_hx* h, const void* q_raw, const void* k_raw, const void* 
     e = attn_fwd_launch(p, s);
     if (e != cudaSuccess) return fail_cuda(h, "attention launch", e);
     h->phase = f2k_hx::kAttended;
+    return F2K_OK;
+}
+
+int f2k_hx_exchange_plan(int world, int seq_local, int heads_per_rank, int n_sms, int* ranges, int max_ranges,
+                         int* n_ranges) {
+    if (world < 1 || world > kMaxQSeg || seq_local < 1 || heads_per_rank < 1 || n_sms < 1 || !n_ranges ||
+        (!ranges && max_ranges > 0))
+        return F2K_ERR_INVALID;
+    ExchangeParams x;
+    std::memset(&x, 0, sizeof x);
+    fill_exchange_order(x, world, seq_local, heads_per_rank, n_sms);
+    for (int i = 0; i < x.n_ranges && i < max_ranges; ++i) {
+        ranges[4 * i + 0] = x.order[i].kind;
+        ranges[4 * i + 1] = x.order[i].step;
+        ranges[4 * i + 2] = x.order[i].sub0;
+        ranges[4 * i + 3] = x.order[i].n;
+    }
+    *n_ranges = x.n_ranges;
+    return F2K_OK;
+}
+
+int f2k_hx_kv_walk_tile(int world, int seq_local, int dst_rank, int token, int* tile) {
+    if (world < 1 || world > kMaxQSeg || seq_local < 1 || dst_rank < 0 || dst_rank >= world || token < 0 ||
+        token >= world * seq_local || !tile)
+        return F2K_ERR_INVALID;
+    *tile = kv_walk_tile(token, dst_rank * seq_local, world * seq_local);
     return F2K_OK;
 }
 

@@ -346,6 +346,18 @@ int f2k_hx_set_wait_limits(f2k_hx* h, long long in_cta_clk, long long peer_clk);
  * f2k_hx_device_status then returns F2K_ERR_DEVICE once, and the next exchange_in is accepted. */
 int f2k_hx_abort(f2k_hx* h);
 
+/* Introspection of f2k_hx_forward's host-side planning; pure arithmetic, no GPU needed (the
+ * tests check its invariants on CPU). No reference counterpart.
+ * f2k_hx_exchange_plan: the order in which a rank's exchange warps take their work: up to
+ * max_ranges entries {kind (0 = Q rows, 1 = K and V rows), ring step (destination = rank - step),
+ * first 16-token block, number of blocks} are written to ranges[4 * i ..], the number of entries
+ * to *n_ranges. Every (kind, step, block) occurs exactly once.
+ * f2k_hx_kv_walk_tile: the 128-token tile of rank dst_rank's K/V walk (its own tokens to the end
+ * of the sequence, then the start) that `token` of the whole sequence belongs to. */
+int f2k_hx_exchange_plan(int world, int seq_local, int heads_per_rank, int n_sms, int* ranges, int max_ranges,
+                         int* n_ranges);
+int f2k_hx_kv_walk_tile(int world, int seq_local, int dst_rank, int token, int* tile);
+
 /* CUDA IPC for the shard buffers: 64-byte handles to pass between the rank processes. */
 int f2k_ipc_export(const void* base, void* handle64);
 int f2k_ipc_open(const void* handle64, void** base);
